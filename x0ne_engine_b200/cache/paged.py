@@ -1,8 +1,9 @@
 """The cache: a slot per sequence, keys and values per run-order entry in pages, per-sequence
 state of fixed size beside them.
 
-Run-order entries whose mixers need the same thing (kv heads, head size, window) form a GROUP
-with storage of its own: one tensor [entries, pages, 2 (K, V), kv_heads, page_size, head_dim], a
+Run-order entries whose mixers need the same thing (kv heads, key and value widths, window) form a
+GROUP with storage of its own: one tensor [entries, pages, 2 (K, V), kv_heads, page_size, head_dim]
+(a flat page of keys then values where the values have another width than the keys, or none), a
 pool of pages and a page table [slots, pages per sequence].  A sequence holds pages only for the
 positions it has (all of them, or a ring that covers its window), so the cache is sized in
 tokens, not in slots x longest sequence.  Entries whose mixers keep a fixed-size state get a
@@ -43,21 +44,28 @@ class KVGroup:
         self.n_pages = n_pages
         self.ring_pages = ring_pages if ring_pages is not None else max_seq_pages
         self.table_stride = self.ring_pages
-        self.storage = torch.zeros((len(entries), n_pages, 2, need.kv_heads, page_size, need.head_dim),
-                                   dtype=dtype, device=device)
+        # values as wide as the keys: [K | V] planes of one shape; else a page is a flat run of elements,
+        # the keys of every kv head first, then the values (none for a mixer that reads them out of its keys)
+        self.v_dim = need.head_dim if need.v_dim is None else int(need.v_dim)
+        if self.v_dim == need.head_dim:
+            shape = (len(entries), n_pages, 2, need.kv_heads, page_size, need.head_dim)
+        else:
+            shape = (len(entries), n_pages, need.kv_heads * page_size * (need.head_dim + self.v_dim))
+        self.storage = torch.zeros(shape, dtype=dtype, device=device)
         self.pool = FreeList(n_pages, "page")
         self.table_host = np.full((n_slots, self.table_stride), -1, dtype=np.int32)
         self.table = torch.full((n_slots, self.table_stride), -1, dtype=torch.int32, device=device)
         self.pages_of: Dict[int, List[int]] = {}
         self._views: Dict[int, PagedCacheArg] = {}
-        page_stride = 2 * need.kv_heads * page_size * need.head_dim
+        page_stride = need.kv_heads * page_size * (need.head_dim + self.v_dim)
+        v_tag = 0 if self.v_dim == need.head_dim else (self.v_dim if self.v_dim > 0 else -1)
         for i, e in enumerate(self.entries):
             self._views[e] = PagedCacheArg(self.storage[i].data_ptr(), self.table.data_ptr(), page_stride,
                                            self.table_stride, self.ring_pages, page_size, need.kv_heads,
-                                           need.head_dim, n_pages)
+                                           need.head_dim, n_pages, v_tag)
 
     def bytes_per_token(self) -> int:
-        return len(self.entries) * 2 * self.need.kv_heads * self.need.head_dim * self.storage.element_size()
+        return len(self.entries) * self.need.kv_heads * (self.need.head_dim + self.v_dim) * self.storage.element_size()
 
     def view(self, entry: int) -> PagedCacheArg:
         return self._views[entry]
@@ -111,13 +119,13 @@ class SequenceCache:
             if reads_cache_of[e] is not None:
                 continue
             if need.kind == "kv":
-                by_key.setdefault((need.kv_heads, need.head_dim, need.window), []).append(e)
+                by_key.setdefault((need.kv_heads, need.head_dim, need.window, need.v_dim), []).append(e)
             elif need.kind == "state":
                 self.states[e] = torch.zeros((self.n_slots,) + tuple(need.state_shape), dtype=torch.float32,
                                              device=device)
             elif need.kind != "none":
                 raise ValueError(f"run-order entry {e}: unknown cache need {need.kind!r}")
-        for (kvh, hd, window), entries in by_key.items():
+        for (kvh, hd, window, _), entries in by_key.items():
             ring = None
             if window is not None:
                 # A pass of c tokens of one sequence writes c new keys before its queries read the

@@ -44,6 +44,8 @@ def detect(config: Mapping[str, Any]) -> str:
     archs = config.get("architectures")
     mt = config.get("model_type")
     by_class = None
+    if archs is None and isinstance(config.get("architecture"), str):
+        archs = [config["architecture"]]          # some checkpoints name their one class under this key
     if archs is not None:
         if not isinstance(archs, list) or len(archs) != 1 or not isinstance(archs[0], str):
             raise ConfigError(f"config.json: architectures must name exactly one class, got {archs!r}")

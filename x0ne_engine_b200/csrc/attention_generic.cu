@@ -15,28 +15,36 @@
 // prompt, in a later chunk, alone or in a batch.
 #include "common.cuh"
 
-#define ATT_MAX_I 8  // head_dim <= 32 * ATT_MAX_I
+//
+// Beyond that (`AttnExtra`): a chunked mask (the query sees its own chunk of positions only), a
+// value width other than the keys', values read out of the key rows, a per-head sink in the
+// denominator, and a per-(row, head) sigmoid gate on the output.  With none of them asked for the
+// operations and their order are the ones above.
+
+#define ATT_MAX_I 16  // value width <= 32 * ATT_MAX_I
 
 template <typename T>
 __global__ void attention_rows_kernel(const T* __restrict__ q, T* __restrict__ out, PagedCache cache,
                                       const int32_t* __restrict__ row_slot, const int32_t* __restrict__ row_pos,
-                                      int n_rows, int q_heads, float scale, int window) {
+                                      int n_rows, int q_heads, float scale, int window, AttnExtra ex) {
     extern __shared__ float smem[];
     pdl_prologue();
     const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
     const int hd = cache.head_dim;
+    const int vd = ex.v_from_k > 0 ? ex.v_from_k : cache_v_dim(cache);
     const int64_t item = (int64_t)blockIdx.x * (blockDim.x >> 5) + w;
     if (item >= (int64_t)n_rows * q_heads) return;
     const int row = (int)(item / q_heads), head = (int)(item % q_heads);
     const int kh = head / (q_heads / cache.kv_heads);
     const int pos = row_pos[row], slot = row_slot[row];
     float* qs = smem + w * hd;
-    const T* qr = q + ((int64_t)row * q_heads + head) * hd;
+    const T* qr = q + (int64_t)row * (ex.q_ld > 0 ? ex.q_ld : (int64_t)q_heads * hd) + (int64_t)head * hd;
     for (int d = lane; d < hd; d += 32) qs[d] = to_f32(qr[d]) * scale;
     __syncwarp();
 
-    const int j_lo = window > 0 ? max(0, pos - window + 1) : 0;
-    const int64_t v_off = (int64_t)cache.kv_heads * cache.page_size * hd;
+    int j_lo = window > 0 ? max(0, pos - window + 1) : 0;
+    if (ex.chunk > 0) j_lo = max(j_lo, pos - pos % ex.chunk);
+    const int64_t v_plane = (int64_t)cache.kv_heads * cache.page_size * hd;
     const T* base = (const T*)cache.base;
     float m = -INFINITY, l = 0.f;
     float acc[ATT_MAX_I];
@@ -68,32 +76,44 @@ __global__ void attention_rows_kernel(const T* __restrict__ q, T* __restrict__ o
             const float pt = __shfl_sync(0xffffffffu, p, t);
             const long long ot = __shfl_sync(0xffffffffu, (long long)off, t);
             if (ot < 0) continue;
-            const T* vr = base + ot + v_off;
+            // the value row of the same position: the key row itself, or the row of the value plane
+            const T* vr = ex.v_from_k > 0 ? base + ot
+                                          : base + (ot - ot % cache.page_stride) + v_plane + ((ot % cache.page_stride) / hd) * vd;
 #pragma unroll
             for (int i = 0; i < ATT_MAX_I; ++i) {
                 const int d = lane + 32 * i;
-                if (d < hd) acc[i] = fmaf(pt, to_f32(vr[d]), acc[i]);
+                if (d < vd) acc[i] = fmaf(pt, to_f32(vr[d]), acc[i]);
             }
         }
         m = m_new;
     }
-    T* o = out + ((int64_t)row * q_heads + head) * hd;
-    const float inv = l > 0.f ? 1.0f / l : 0.f;      // a row with no readable key (a padding row) gets zeros
+    if (ex.sink != nullptr && slot >= 0) {
+        const float sk = ex.sink[head];
+        const float m_new = fmaxf(m, sk);
+        const float alpha = expf(m - m_new);
+        l = l * alpha + expf(sk - m_new);
+#pragma unroll
+        for (int i = 0; i < ATT_MAX_I; ++i) acc[i] *= alpha;
+    }
+    T* o = out + ((int64_t)row * q_heads + head) * vd;
+    float inv = l > 0.f ? 1.0f / l : 0.f;      // a row with no readable key (a padding row) gets zeros
+    if (ex.gate != nullptr) inv *= 1.0f / (1.0f + expf(-to_f32(((const T*)ex.gate)[(int64_t)row * ex.gate_ld + head])));
 #pragma unroll
     for (int i = 0; i < ATT_MAX_I; ++i) {
         const int d = lane + 32 * i;
-        if (d < hd) o[d] = from_f32<T>(acc[i] * inv);
+        if (d < vd) o[d] = from_f32<T>(acc[i] * inv);
     }
 }
 
-X0NE_API int x0ne_attention_rows(const void* q, void* out, int dt, PagedCache cache, const int32_t* row_slot,
-                                 const int32_t* row_pos, int n_rows, int q_heads, float scale, int window,
-                                 cudaStream_t stream) {
+X0NE_API int x0ne_attention_rows_ex(const void* q, void* out, int dt, PagedCache cache, const int32_t* row_slot,
+                                    const int32_t* row_pos, int n_rows, int q_heads, float scale, int window,
+                                    AttnExtra ex, cudaStream_t stream) {
     X0NE_REQUIRE(n_rows >= 0 && q_heads > 0 && cache.kv_heads > 0 && q_heads % cache.kv_heads == 0,
                  "attention: %d q heads over %d kv heads", q_heads, cache.kv_heads);
-    X0NE_REQUIRE(cache.head_dim > 0 && cache.head_dim <= 32 * ATT_MAX_I,
-                 "attention: head_dim %d is beyond the plain kernel's limit of %d", cache.head_dim, 32 * ATT_MAX_I);
-    X0NE_REQUIRE(window >= 0, "attention: negative window");
+    const int vd = ex.v_from_k > 0 ? ex.v_from_k : cache_v_dim(cache);
+    X0NE_REQUIRE(cache.head_dim > 0 && cache.head_dim <= 2048 && vd > 0 && vd <= 32 * ATT_MAX_I && ex.v_from_k <= cache.head_dim,
+                 "attention: keys of %d and values of %d are beyond the plain kernel's limits of 2048 and %d", cache.head_dim, vd, 32 * ATT_MAX_I);
+    X0NE_REQUIRE(window >= 0 && ex.chunk >= 0, "attention: negative window or chunk");
     if (n_rows == 0) return 0;
     const int warps = 4;
     const int64_t items = (int64_t)n_rows * q_heads;
@@ -101,11 +121,18 @@ X0NE_API int x0ne_attention_rows(const void* q, void* out, int dt, PagedCache ca
     const size_t smem = (size_t)warps * cache.head_dim * sizeof(float);
     if (dt == X0NE_F32)
         x0ne_launch(attention_rows_kernel<float>, dim3(grid), dim3(warps * 32), smem, stream, (const float*)q, (float*)out, cache, row_slot,
-                                                                       row_pos, n_rows, q_heads, scale, window);
+                                                                       row_pos, n_rows, q_heads, scale, window, ex);
     else if (dt == X0NE_BF16)
         x0ne_launch(attention_rows_kernel<bf16>, dim3(grid), dim3(warps * 32), smem, stream, (const bf16*)q, (bf16*)out, cache, row_slot,
-                                                                      row_pos, n_rows, q_heads, scale, window);
+                                                                      row_pos, n_rows, q_heads, scale, window, ex);
     else
         X0NE_REQUIRE(false, "attention: unknown dtype tag %d", dt);
     X0NE_LAUNCH_CHECK();
+}
+
+X0NE_API int x0ne_attention_rows(const void* q, void* out, int dt, PagedCache cache, const int32_t* row_slot,
+                                 const int32_t* row_pos, int n_rows, int q_heads, float scale, int window,
+                                 cudaStream_t stream) {
+    AttnExtra none = {};
+    return x0ne_attention_rows_ex(q, out, dt, cache, row_slot, row_pos, n_rows, q_heads, scale, window, none, stream);
 }

@@ -163,8 +163,10 @@ __device__ __forceinline__ float block_sum(float v, float* sh) { return block_re
 __device__ __forceinline__ float block_max(float v, float* sh) { return block_reduce(v, sh, OpMax(), -INFINITY); }
 
 // The paged cache of one run-order entry.  A page holds `page_size` positions of every kv
-// head, K then V: [2][kv_heads][page_size][head_dim].  A sequence's logical page
-// (pos / page_size) % ring_pages is found in its row of the page table.
+// head, K then V: [kv_heads][page_size][head_dim] keys, then [kv_heads][page_size][v width]
+// values.  The values are as wide as the keys unless `v_dim` says otherwise (0: as wide as the
+// keys; negative: the page holds no values, a mixer whose values are a part of its keys).  A
+// sequence's logical page (pos / page_size) % ring_pages is found in its row of the page table.
 struct PagedCache {
     void* base;                 // first page of this entry
     const int32_t* page_table;  // [slots][table_stride]
@@ -175,6 +177,19 @@ struct PagedCache {
     int32_t kv_heads;
     int32_t head_dim;
     int32_t n_pages;            // pages in the pool, for the bounds check
+    int32_t v_dim;              // width of a value row: 0 = head_dim, negative = no values are kept
+};
+
+__host__ __device__ __forceinline__ int cache_v_dim(const PagedCache& c) { return c.v_dim == 0 ? c.head_dim : (c.v_dim > 0 ? c.v_dim : 0); }
+
+// What an attention kernel may be asked for beyond causal softmax over a window.  All zero: nothing.
+struct AttnExtra {
+    int32_t chunk;        // > 0: a query sees the keys of its own chunk of this many positions only
+    int32_t v_from_k;     // > 0: the values are the first v_from_k values of the key rows (no value plane is read)
+    const float* sink;    // per q head, or null: exp(sink) joins the softmax denominator once (no key, no value, unscaled)
+    const void* gate;     // per (row, q head) in the activation type, or null: the head's output is multiplied by sigmoid(gate)
+    int64_t gate_ld;      // values between the gates of consecutive rows
+    int64_t q_ld;         // values between consecutive query rows (0: q heads x head_dim)
 };
 
 // Element offset of (slot, pos, kv head, which = 0 for K / 1 for V); -1 if there is no page, or if
@@ -184,6 +199,7 @@ __device__ __forceinline__ int64_t cache_row_offset(const PagedCache& c, int slo
     const int lp = (pos / c.page_size) % c.ring_pages;
     const int page = c.page_table[(int64_t)slot * c.table_stride + lp];
     if (page < 0 || page >= c.n_pages) return -1;
-    return (int64_t)page * c.page_stride +
-           (((int64_t)which * c.kv_heads + kv_head) * c.page_size + (pos % c.page_size)) * c.head_dim;
+    if (which == 0) return (int64_t)page * c.page_stride + ((int64_t)kv_head * c.page_size + (pos % c.page_size)) * c.head_dim;
+    return (int64_t)page * c.page_stride + (int64_t)c.kv_heads * c.page_size * c.head_dim +
+           ((int64_t)kv_head * c.page_size + (pos % c.page_size)) * cache_v_dim(c);
 }

@@ -40,7 +40,7 @@ bool x0ne_pdl_enabled() {
 // parked in shared memory between the two sweeps when it fits there (`keep` floats of dynamic
 // shared memory, 0 if it does not), so the residual is read once.
 template <typename T>
-__global__ void add_rmsnorm_any_kernel(float* __restrict__ resid, const T* __restrict__ delta,
+__global__ void add_rmsnorm_any_kernel(float* __restrict__ resid, const T* __restrict__ delta, const T* __restrict__ delta2,
                                        const float* __restrict__ w, T* __restrict__ out,
                                        const int32_t* __restrict__ rows, int hidden, float eps, int keep) {
     extern __shared__ float parked[];
@@ -52,7 +52,8 @@ __global__ void add_rmsnorm_any_kernel(float* __restrict__ resid, const T* __res
     for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
         float v = r[i];
         if (delta) {
-            v = v + to_f32(delta[src * hidden + i]);     // one IEEE add, stored back
+            // one IEEE add, stored back; two branches of a parallel layer are summed first
+            v = v + (delta2 ? to_f32(delta[src * hidden + i]) + to_f32(delta2[src * hidden + i]) : to_f32(delta[src * hidden + i]));
             r[i] = v;
         }
         if (i < keep) parked[i] = v;
@@ -118,7 +119,7 @@ __device__ __forceinline__ void copy2(bf16* d, const bf16* s) { *reinterpret_cas
 
 // ITS: how many sweeps of the block cover a row (1, 2 or VEC_IT).
 template <typename T, int ITS>
-__global__ void add_rmsnorm_vec_kernel(float* __restrict__ resid, const T* __restrict__ delta,
+__global__ void add_rmsnorm_vec_kernel(float* __restrict__ resid, const T* __restrict__ delta, const T* __restrict__ delta2,
                                        const float* __restrict__ w, T* __restrict__ out,
                                        const int32_t* __restrict__ rows, int hidden, float eps) {
     __shared__ float sh[32];
@@ -140,6 +141,7 @@ __global__ void add_rmsnorm_vec_kernel(float* __restrict__ resid, const T* __res
     pdl_wait();
     float* r = resid + src * hidden;
     const T* d = delta ? delta + src * hidden : nullptr;
+    const T* d2 = delta && delta2 ? delta2 + src * hidden : nullptr;
     T* o = out + (int64_t)blockIdx.x * hidden;
     float v[ITS][8];
     float ss = 0.f;
@@ -151,6 +153,12 @@ __global__ void add_rmsnorm_vec_kernel(float* __restrict__ resid, const T* __res
             if (d) {
                 float dv[8];
                 load8(d + i, dv);
+                if (d2) {
+                    float dw[8];
+                    load8(d2 + i, dw);
+#pragma unroll
+                    for (int k = 0; k < 8; ++k) dv[k] = dv[k] + dw[k];
+                }
 #pragma unroll
                 for (int k = 0; k < 8; ++k) v[it][k] = v[it][k] + dv[k];
                 store8(r + i, v[it]);
@@ -175,30 +183,32 @@ __global__ void add_rmsnorm_vec_kernel(float* __restrict__ resid, const T* __res
 }
 
 template <typename T>
-static void launch_add_rmsnorm_vec(float* resid, const T* delta, const float* w, T* out, const int32_t* rows, int n_rows,
+static void launch_add_rmsnorm_vec(float* resid, const T* delta, const T* delta2, const float* w, T* out, const int32_t* rows, int n_rows,
                                    int hidden, float eps, int threads, cudaStream_t stream) {
     const int sweeps = (hidden / 8 + threads - 1) / threads;
     if (sweeps <= 1)
-        x0ne_launch(add_rmsnorm_vec_kernel<T, 1>, dim3(n_rows), dim3(threads), 0, stream, resid, delta, w, out, rows, hidden, eps);
+        x0ne_launch(add_rmsnorm_vec_kernel<T, 1>, dim3(n_rows), dim3(threads), 0, stream, resid, delta, delta2, w, out, rows, hidden, eps);
     else if (sweeps == 2)
-        x0ne_launch(add_rmsnorm_vec_kernel<T, 2>, dim3(n_rows), dim3(threads), 0, stream, resid, delta, w, out, rows, hidden, eps);
+        x0ne_launch(add_rmsnorm_vec_kernel<T, 2>, dim3(n_rows), dim3(threads), 0, stream, resid, delta, delta2, w, out, rows, hidden, eps);
     else
-        x0ne_launch(add_rmsnorm_vec_kernel<T, VEC_IT>, dim3(n_rows), dim3(threads), 0, stream, resid, delta, w, out, rows, hidden, eps);
+        x0ne_launch(add_rmsnorm_vec_kernel<T, VEC_IT>, dim3(n_rows), dim3(threads), 0, stream, resid, delta, delta2, w, out, rows, hidden, eps);
 }
 
-X0NE_API int x0ne_add_rmsnorm(float* resid, const void* delta, const float* w, void* out, int dt,
-                              const int32_t* rows, int n_rows, int hidden, float eps, cudaStream_t stream) {
+// `delta2`, if given with `delta`, is a second branch's result: r = resid + (f32(delta) + f32(delta2)).
+X0NE_API int x0ne_add2_rmsnorm(float* resid, const void* delta, const void* delta2, const float* w, void* out, int dt,
+                               const int32_t* rows, int n_rows, int hidden, float eps, cudaStream_t stream) {
     X0NE_REQUIRE(n_rows >= 0 && hidden > 0, "add_rmsnorm: rows %d hidden %d", n_rows, hidden);
+    X0NE_REQUIRE(delta != nullptr || delta2 == nullptr, "add_rmsnorm: a second delta without a first");
     if (n_rows == 0) return 0;
     if (hidden % 8 == 0 && hidden <= 8 * 1024 * VEC_IT &&
-        ((((uintptr_t)resid | (uintptr_t)delta | (uintptr_t)w | (uintptr_t)out) & 15) == 0)) {
+        ((((uintptr_t)resid | (uintptr_t)delta | (uintptr_t)delta2 | (uintptr_t)w | (uintptr_t)out) & 15) == 0)) {
         int threads = (hidden / 8 + 31) / 32 * 32;
         if (threads > 1024) threads = 1024;
         if (hidden / 8 > 512 && hidden / 8 <= 1024) threads = 512;   // two sweeps of 512 rather than one of 1024
         if (dt == X0NE_F32)
-            launch_add_rmsnorm_vec<float>(resid, (const float*)delta, w, (float*)out, rows, n_rows, hidden, eps, threads, stream);
+            launch_add_rmsnorm_vec<float>(resid, (const float*)delta, (const float*)delta2, w, (float*)out, rows, n_rows, hidden, eps, threads, stream);
         else if (dt == X0NE_BF16)
-            launch_add_rmsnorm_vec<bf16>(resid, (const bf16*)delta, w, (bf16*)out, rows, n_rows, hidden, eps, threads, stream);
+            launch_add_rmsnorm_vec<bf16>(resid, (const bf16*)delta, (const bf16*)delta2, w, (bf16*)out, rows, n_rows, hidden, eps, threads, stream);
         else
             X0NE_REQUIRE(false, "add_rmsnorm: unknown dtype tag %d", dt);
         X0NE_LAUNCH_CHECK();
@@ -207,12 +217,17 @@ X0NE_API int x0ne_add_rmsnorm(float* resid, const void* delta, const float* w, v
     const int keep = hidden <= 10240 ? hidden : 0;        // up to 40 KB of dynamic shared memory
     const size_t smem = (size_t)keep * sizeof(float);
     if (dt == X0NE_F32)
-        x0ne_launch(add_rmsnorm_any_kernel<float>, dim3(n_rows), dim3(block), smem, stream, resid, (const float*)delta, w, (float*)out, rows, hidden, eps, keep);
+        x0ne_launch(add_rmsnorm_any_kernel<float>, dim3(n_rows), dim3(block), smem, stream, resid, (const float*)delta, (const float*)delta2, w, (float*)out, rows, hidden, eps, keep);
     else if (dt == X0NE_BF16)
-        x0ne_launch(add_rmsnorm_any_kernel<bf16>, dim3(n_rows), dim3(block), smem, stream, resid, (const bf16*)delta, w, (bf16*)out, rows, hidden, eps, keep);
+        x0ne_launch(add_rmsnorm_any_kernel<bf16>, dim3(n_rows), dim3(block), smem, stream, resid, (const bf16*)delta, (const bf16*)delta2, w, (bf16*)out, rows, hidden, eps, keep);
     else
         X0NE_REQUIRE(false, "add_rmsnorm: unknown dtype tag %d", dt);
     X0NE_LAUNCH_CHECK();
+}
+
+X0NE_API int x0ne_add_rmsnorm(float* resid, const void* delta, const float* w, void* out, int dt,
+                              const int32_t* rows, int n_rows, int hidden, float eps, cudaStream_t stream) {
+    return x0ne_add2_rmsnorm(resid, delta, nullptr, w, out, dt, rows, n_rows, hidden, eps, stream);
 }
 
 // ----------------------------------------------------------------------------------------

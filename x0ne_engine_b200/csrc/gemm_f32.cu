@@ -19,10 +19,13 @@
 
 __global__ void __launch_bounds__(256) gemm_f32_nt_kernel(const float* __restrict__ A, const float* __restrict__ W,
                                                            float* __restrict__ C, int M, int N, int K, int lda,
-                                                           int ldw, int ldc) {
+                                                           int ldw, int ldc, int64_t sa, int64_t sw, int64_t sc) {
     __shared__ float As[BK][BM + 4];
     __shared__ float Ws[BK][BN + 4];
     pdl_prologue();
+    A += blockIdx.z * sa;       // one product per z: a batch of independent products of one shape
+    W += blockIdx.z * sw;
+    C += blockIdx.z * sc;
     const int tid = threadIdx.x;
     const int m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
     const int tx = tid % 16, ty = tid / 16;  // tx: 16 column groups of 4, ty: 16 row groups of 8
@@ -76,13 +79,20 @@ __global__ void __launch_bounds__(256) gemm_f32_nt_kernel(const float* __restric
     }
 }
 
-X0NE_API int x0ne_gemm_f32_nt(const float* A, const float* W, float* C, int M, int N, int K, int lda, int ldw, int ldc,
-                              cudaStream_t stream) {
+// `batch` products of one shape: product b reads A + b sa and W + b sw and writes C + b sc.
+X0NE_API int x0ne_gemm_f32_nt_batched(const float* A, const float* W, float* C, int M, int N, int K, int lda, int ldw, int ldc,
+                                      int batch, int64_t sa, int64_t sw, int64_t sc, cudaStream_t stream) {
     X0NE_REQUIRE(M >= 0 && N > 0 && K > 0 && lda >= K && ldw >= K && ldc >= N, "gemm_f32: M %d N %d K %d lda %d ldw %d ldc %d",
                  M, N, K, lda, ldw, ldc);
+    X0NE_REQUIRE(batch >= 1 && batch <= 65535, "gemm_f32: batch %d", batch);
     if (M == 0) return 0;
-    dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM);
+    dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM, batch);
     X0NE_REQUIRE(grid.y <= 65535, "gemm_f32: M %d needs more than 65535 row tiles", M);
-    x0ne_launch(gemm_f32_nt_kernel, dim3(grid), dim3(256), 0, stream, A, W, C, M, N, K, lda, ldw, ldc);
+    x0ne_launch(gemm_f32_nt_kernel, dim3(grid), dim3(256), 0, stream, A, W, C, M, N, K, lda, ldw, ldc, sa, sw, sc);
     X0NE_LAUNCH_CHECK();
+}
+
+X0NE_API int x0ne_gemm_f32_nt(const float* A, const float* W, float* C, int M, int N, int K, int lda, int ldw, int ldc,
+                              cudaStream_t stream) {
+    return x0ne_gemm_f32_nt_batched(A, W, C, M, N, K, lda, ldw, ldc, 1, 0, 0, 0, stream);
 }

@@ -1,0 +1,182 @@
+// Row-wise kernels of mixers and feed-forwards beyond the pre-norm GQA block: a clipped gated
+// activation, the cache write of an attention whose values are blended with an earlier layer's,
+// and the preparation of a latent attention's queries and cache rows (latent norm, interleaved
+// rotary pairs with a per-pair frequency table).  Templated on the activation type like the
+// kernels of elementwise.cu; per-channel weights, angles, norms and blends are float32.
+#include "common.cuh"
+
+// ----------------------------------------------------------------------------------------
+// Clipped gated activation on the packed [gate; up] row:
+//   g = min(gate, limit); u = clamp(up, -limit, limit); out = g * sigmoid(slope * g) * (u + shift)
+// ----------------------------------------------------------------------------------------
+template <typename T>
+__global__ void glu_clipped_kernel(const T* __restrict__ gate_up, T* __restrict__ out, int inter, int64_t total, float limit,
+                                   float slope, float shift) {
+    pdl_prologue();
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t row = i / inter;
+        const int col = (int)(i % inter);
+        const float g = fminf(to_f32(gate_up[row * 2 * inter + col]), limit);
+        const float u = fminf(fmaxf(to_f32(gate_up[row * 2 * inter + inter + col]), -limit), limit);
+        out[i] = from_f32<T>(g / (1.0f + expf(-slope * g)) * (u + shift));
+    }
+}
+
+X0NE_API int x0ne_glu_clipped(const void* gate_up, void* out, int dt, int n_rows, int inter, float limit, float slope,
+                              float shift, cudaStream_t stream) {
+    X0NE_REQUIRE(n_rows >= 0 && inter > 0 && limit > 0.f, "glu_clipped: rows %d width %d limit %g", n_rows, inter, limit);
+    if (n_rows == 0) return 0;
+    const int64_t total = (int64_t)n_rows * inter;
+    const unsigned grid = (unsigned)((total + 255) / 256 < 65535 * 16 ? (total + 255) / 256 : 65535 * 16);
+    if (dt == X0NE_F32)
+        x0ne_launch(glu_clipped_kernel<float>, dim3(grid), dim3(256), 0, stream, (const float*)gate_up, (float*)out, inter, total, limit, slope, shift);
+    else if (dt == X0NE_BF16)
+        x0ne_launch(glu_clipped_kernel<bf16>, dim3(grid), dim3(256), 0, stream, (const bf16*)gate_up, (bf16*)out, inter, total, limit, slope, shift);
+    else
+        X0NE_REQUIRE(false, "glu_clipped: unknown dtype tag %d", dt);
+    X0NE_LAUNCH_CHECK();
+}
+
+// ----------------------------------------------------------------------------------------
+// K/V write of an attention without rotation.  `src` holds, per row of `ld` values, the keys at
+// column k_col (kv_heads x k_dim) and the values at column v_col (kv_heads x v_dim).
+//   mode 0: keys and values go to the cache as they are.
+//   mode 1: the same, and the values are also kept in `v_first` (rows of kv_heads x v_dim) for
+//           the later layers of this pass.
+//   mode 2: v = (1 - lambda) v + lambda v_first[row] in float32, lambda read from the device.
+// One block per row; a row whose position has no page (or whose slot is negative) writes nothing
+// into the cache.
+// ----------------------------------------------------------------------------------------
+template <typename T>
+__global__ void kv_write_blend_kernel(const T* __restrict__ src, int ld, int k_col, int v_col, T* __restrict__ v_first,
+                                      const float* __restrict__ lambda, int mode, PagedCache cache,
+                                      const int32_t* __restrict__ row_slot, const int32_t* __restrict__ row_pos) {
+    pdl_launch_dependents();
+    const float lam = mode == 2 ? lambda[0] : 0.f;
+    const int row = blockIdx.x;
+    const int slot = row_slot[row], pos = row_pos[row];
+    pdl_wait();
+    const int kd = cache.head_dim, vd = cache_v_dim(cache), kvh = cache.kv_heads;
+    T* base = (T*)cache.base;
+    const T* s = src + (int64_t)row * ld;
+    const int64_t k0 = cache_row_offset(cache, slot, pos, 0, 0);
+    const int64_t head_k = (int64_t)cache.page_size * kd, head_v = (int64_t)cache.page_size * vd;
+    if (k0 >= 0)
+        for (int i = threadIdx.x; i < kvh * kd; i += blockDim.x) base[k0 + (i / kd) * head_k + (i % kd)] = s[k_col + i];
+    const int64_t v0 = cache_row_offset(cache, slot, pos, 0, 1);
+    for (int i = threadIdx.x; i < kvh * vd; i += blockDim.x) {
+        T v = s[v_col + i];
+        if (mode == 1) v_first[(int64_t)row * kvh * vd + i] = v;
+        if (mode == 2) v = from_f32<T>((1.0f - lam) * to_f32(v) + lam * to_f32(v_first[(int64_t)row * kvh * vd + i]));
+        if (v0 >= 0) base[v0 + (i / vd) * head_v + (i % vd)] = v;
+    }
+}
+
+X0NE_API int x0ne_kv_write_blend(const void* src, int dt, int ld, int k_col, int v_col, void* v_first, const float* lambda,
+                                 int mode, PagedCache cache, const int32_t* row_slot, const int32_t* row_pos, int n_rows,
+                                 cudaStream_t stream) {
+    X0NE_REQUIRE(n_rows >= 0 && ld > 0 && k_col >= 0 && v_col >= 0 && mode >= 0 && mode <= 2, "kv_write: rows %d ld %d mode %d", n_rows, ld, mode);
+    X0NE_REQUIRE(cache.v_dim >= 0, "kv_write: the cache keeps no values");
+    X0NE_REQUIRE(k_col + cache.kv_heads * cache.head_dim <= ld && v_col + cache.kv_heads * cache_v_dim(cache) <= ld,
+                 "kv_write: keys or values lie outside the source rows");
+    X0NE_REQUIRE(mode == 0 || v_first != nullptr, "kv_write: mode %d needs the buffer of first values", mode);
+    X0NE_REQUIRE(mode != 2 || lambda != nullptr, "kv_write: blending needs its weight");
+    if (n_rows == 0) return 0;
+    if (dt == X0NE_F32)
+        x0ne_launch(kv_write_blend_kernel<float>, dim3(n_rows), dim3(128), 0, stream, (const float*)src, ld, k_col, v_col, (float*)v_first, lambda, mode, cache, row_slot, row_pos);
+    else if (dt == X0NE_BF16)
+        x0ne_launch(kv_write_blend_kernel<bf16>, dim3(n_rows), dim3(128), 0, stream, (const bf16*)src, ld, k_col, v_col, (bf16*)v_first, lambda, mode, cache, row_slot, row_pos);
+    else
+        X0NE_REQUIRE(false, "kv_write: unknown dtype tag %d", dt);
+    X0NE_LAUNCH_CHECK();
+}
+
+// ----------------------------------------------------------------------------------------
+// Latent attention, preparation of a pass's rows.  `src` holds per row of `ld` values the queries
+// at column 0 (heads x (dim + rot)) and, at column dkv_col, `rank` latent values followed by `rot`
+// values of the key part that all heads share.
+//   c = latent * rsqrt(mean(latent^2) + eps) * w        -> cache row [0, rank)
+//   shared key part, rotated                             -> cache row [rank, rank + rot)
+//   q_out[row][head] = [ q_abs[head][row][0..rank) , rotated q[row][head][dim..dim+rot) ]
+// where q_abs (heads x rows_stride x rank) holds each head's unrotated query already multiplied
+// into the latent space, so that a score is one dot product of rank + rot values with the cache
+// row.  Rotation: pair (2i, 2i+1) turns by pos * freq[i]; cos and sin are scaled by `mag`.
+// `table` (float32 [positions][rot]: rot/2 cosines then rot/2 sines, already scaled) replaces the
+// computation for the positions it covers.  One block per row.
+// ----------------------------------------------------------------------------------------
+template <typename T>
+__global__ void latent_prepare_kernel(const T* __restrict__ src, int ld, int dkv_col, const T* __restrict__ q_abs,
+                                      int64_t q_abs_head_stride, const float* __restrict__ norm_w, float eps,
+                                      const float* __restrict__ freq, float mag, const float* __restrict__ table,
+                                      int table_positions, T* __restrict__ q_out, int heads, int dim, int rot, int rank,
+                                      PagedCache cache, const int32_t* __restrict__ row_slot,
+                                      const int32_t* __restrict__ row_pos, int write_cache) {
+    extern __shared__ float cs[];          // rot/2 cosines, rot/2 sines
+    __shared__ float partial[32];
+    pdl_launch_dependents();
+    const int row = blockIdx.x;
+    const int slot = row_slot[row], pos = row_pos[row];
+    const int half = rot / 2;
+    for (int i = threadIdx.x; i < half; i += blockDim.x) {
+        if (pos >= 0 && pos < table_positions) {
+            cs[i] = table[(int64_t)pos * rot + i];
+            cs[half + i] = table[(int64_t)pos * rot + half + i];
+        } else {
+            float sn, c;
+            sincosf((float)pos * freq[i], &sn, &c);
+            cs[i] = c * mag;
+            cs[half + i] = sn * mag;
+        }
+    }
+    pdl_wait();
+    const T* s = src + (int64_t)row * ld;
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < rank; i += blockDim.x) {
+        const float v = to_f32(s[dkv_col + i]);
+        ss = fmaf(v, v, ss);
+    }
+    const float scale = 1.0f / sqrtf(block_reduce(ss, partial, OpSum(), 0.f) / (float)rank + eps);   // (syncs: cs is complete)
+    const int64_t k0 = write_cache ? cache_row_offset(cache, slot, pos, 0, 0) : -1;
+    if (k0 >= 0) {
+        T* kr = (T*)cache.base + k0;
+        for (int i = threadIdx.x; i < rank; i += blockDim.x) kr[i] = from_f32<T>(to_f32(s[dkv_col + i]) * scale * norm_w[i]);
+        for (int i = threadIdx.x; i < half; i += blockDim.x) {
+            const float u = to_f32(s[dkv_col + rank + 2 * i]), v = to_f32(s[dkv_col + rank + 2 * i + 1]);
+            kr[rank + 2 * i] = from_f32<T>(u * cs[i] - v * cs[half + i]);
+            kr[rank + 2 * i + 1] = from_f32<T>(v * cs[i] + u * cs[half + i]);
+        }
+    }
+    const int qw = rank + rot;
+    T* qo = q_out + (int64_t)row * heads * qw;
+    for (int i = threadIdx.x; i < heads * rank; i += blockDim.x) {
+        const int h = i / rank, d = i % rank;
+        qo[h * qw + d] = q_abs[h * q_abs_head_stride + (int64_t)row * rank + d];
+    }
+    for (int i = threadIdx.x; i < heads * half; i += blockDim.x) {
+        const int h = i / half, j = i % half;
+        const T* qr = s + h * (dim + rot) + dim;
+        const float u = to_f32(qr[2 * j]), v = to_f32(qr[2 * j + 1]);
+        qo[h * qw + rank + 2 * j] = from_f32<T>(u * cs[j] - v * cs[half + j]);
+        qo[h * qw + rank + 2 * j + 1] = from_f32<T>(v * cs[j] + u * cs[half + j]);
+    }
+}
+
+X0NE_API int x0ne_latent_prepare(const void* src, int dt, int ld, int dkv_col, const void* q_abs, int64_t q_abs_head_stride,
+                                 const float* norm_w, float eps, const float* freq, float mag, const float* table,
+                                 int table_positions, void* q_out, int heads, int dim, int rot, int rank, PagedCache cache,
+                                 const int32_t* row_slot, const int32_t* row_pos, int n_rows, int write_cache,
+                                 cudaStream_t stream) {
+    X0NE_REQUIRE(n_rows >= 0 && heads > 0 && dim > 0 && rot >= 0 && rot % 2 == 0 && rank > 0, "latent_prepare: heads %d dim %d rot %d rank %d", heads, dim, rot, rank);
+    X0NE_REQUIRE(cache.kv_heads == 1 && cache.head_dim == rank + rot, "latent_prepare: the cache row is %d x %d, not 1 x %d", cache.kv_heads, cache.head_dim, rank + rot);
+    X0NE_REQUIRE(heads * (dim + rot) <= dkv_col && dkv_col + rank + rot <= ld, "latent_prepare: columns lie outside the source rows");
+    X0NE_REQUIRE(rot == 0 || freq != nullptr, "latent_prepare: no frequencies");
+    if (n_rows == 0) return 0;
+    const size_t smem = (size_t)(rot > 0 ? rot : 2) * sizeof(float);
+    if (dt == X0NE_F32)
+        x0ne_launch(latent_prepare_kernel<float>, dim3(n_rows), dim3(256), smem, stream, (const float*)src, ld, dkv_col, (const float*)q_abs, q_abs_head_stride, norm_w, eps, freq, mag, table, table_positions, (float*)q_out, heads, dim, rot, rank, cache, row_slot, row_pos, write_cache);
+    else if (dt == X0NE_BF16)
+        x0ne_launch(latent_prepare_kernel<bf16>, dim3(n_rows), dim3(256), smem, stream, (const bf16*)src, ld, dkv_col, (const bf16*)q_abs, q_abs_head_stride, norm_w, eps, freq, mag, table, table_positions, (bf16*)q_out, heads, dim, rot, rank, cache, row_slot, row_pos, write_cache);
+    else
+        X0NE_REQUIRE(false, "latent_prepare: unknown dtype tag %d", dt);
+    X0NE_LAUNCH_CHECK();
+}

@@ -34,7 +34,27 @@ class PagedCacheArg(Structure):
     """Mirror of `struct PagedCache` in common.cuh."""
     _fields_ = [("base", c_void_p), ("page_table", c_void_p), ("page_stride", c_int64),
                 ("table_stride", c_int32), ("ring_pages", c_int32), ("page_size", c_int32),
-                ("kv_heads", c_int32), ("head_dim", c_int32), ("n_pages", c_int32)]
+                ("kv_heads", c_int32), ("head_dim", c_int32), ("n_pages", c_int32), ("v_dim", c_int32)]
+
+    @property
+    def value_dim(self) -> int:
+        """Width of a cached value row (0 when the page keeps no values)."""
+        return self.head_dim if self.v_dim == 0 else max(int(self.v_dim), 0)
+
+
+class AttnExtraArg(Structure):
+    """Mirror of `struct AttnExtra` in common.cuh: what an attention kernel is asked for beyond causal
+    softmax over a window (all zero: nothing)."""
+    _fields_ = [("chunk", c_int32), ("v_from_k", c_int32), ("sink", c_void_p), ("gate", c_void_p),
+                ("gate_ld", c_int64), ("q_ld", c_int64)]
+
+
+def attn_extra(chunk: int = 0, v_from_k: int = 0, sink: Optional[torch.Tensor] = None, gate: Optional[torch.Tensor] = None,
+               gate_ld: int = 0, q_ld: int = 0) -> AttnExtraArg:
+    """`sink`: float32 per q head.  `gate`: a view whose element (row, head) lies at row * gate_ld + head."""
+    if sink is not None:
+        _need(sink, torch.float32, "sink")
+    return AttnExtraArg(int(chunk or 0), int(v_from_k or 0), _ptr(sink), _ptr(gate), int(gate_ld), int(q_ld))
 
 
 class SampleIOArg(Structure):
@@ -55,6 +75,14 @@ _P, _I, _F, _L = c_void_p, c_int, c_float, c_int64
 _SIGNATURES = {
     "x0ne_embedding": [_P, _I, _P, _P, _I, _I, _I, _P],
     "x0ne_add_rmsnorm": [_P, _P, _P, _P, _I, _P, _I, _I, _F, _P],
+    "x0ne_add2_rmsnorm": [_P, _P, _P, _P, _P, _I, _P, _I, _I, _F, _P],
+    "x0ne_glu_clipped": [_P, _P, _I, _I, _I, _F, _F, _F, _P],
+    "x0ne_kv_write_blend": [_P, _I, _I, _I, _I, _P, _P, _I, None, _P, _P, _I, _P],
+    "x0ne_latent_prepare": [_P, _I, _I, _I, _P, _L, _P, _F, _P, _F, _P, _I, _P, _I, _I, _I, _I, None, _P, _P, _I, _I, _P],
+    "x0ne_attention_rows_ex": [_P, _P, _I, None, _P, _P, _I, _I, _F, _I, "ex", _P],
+    "x0ne_gemm_f32_nt_batched": [_P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _L, _L, _L, _P],
+    "x0ne_attention_flex_prefill": [_P, _P, None, _P, _P, _I, _P, _P, _P, _I, _F, _I, "ex", _P],
+    "x0ne_attention_flex_decode": [_P, _P, None, _P, _P, _I, _I, _F, _I, "ex", _I, _P, _L, _P],
     "x0ne_qk_norm_rope_kv_write": [_P, _I, _P, _P, _P, _I, _P, None, _P, _P, _I, _I, _F, _I, _P, _I, _P],
     "x0ne_swiglu": [_P, _P, _I, _I, _I, _P],
     "x0ne_attention_rows": [_P, _P, _I, None, _P, _P, _I, _I, _F, _I, _P],
@@ -80,7 +108,8 @@ def _lib(name: str) -> ctypes.CDLL:
             fn = getattr(lib, fn_name, None)
             if fn is not None:
                 # None: the cache view, by value; "io": the sampler's arguments, by value
-                fn.argtypes = [PagedCacheArg if a is None else SampleIOArg if a == "io" else a for a in args]
+                fn.argtypes = [PagedCacheArg if a is None else SampleIOArg if a == "io" else AttnExtraArg if a == "ex" else a
+                               for a in args]
                 fn.restype = c_int
         _libs[name] = lib
     return lib
@@ -155,10 +184,19 @@ def embedding(table: torch.Tensor, tokens: torch.Tensor, resid: torch.Tensor, n_
                                    n_rows, hidden, vocab, _stream()), "embedding")
 
 
-def add_rmsnorm(resid: torch.Tensor, delta: Optional[torch.Tensor], weight: torch.Tensor, out: torch.Tensor,
+def add_rmsnorm(resid: torch.Tensor, delta, weight: torch.Tensor, out: torch.Tensor,
                 n_rows: int, eps: float, rows: Optional[torch.Tensor] = None) -> None:
-    """resid += delta (if given); out = rmsnorm(resid) * weight.  `rows` gathers source rows."""
+    """resid += delta (if given); out = rmsnorm(resid) * weight.  `rows` gathers source rows.  `delta` may
+    be a pair of tensors, the results of two branches that read the same normed rows: their float32
+    sum is added."""
     lib = _lib("core")
+    delta2 = None
+    if isinstance(delta, (tuple, list)):
+        parts = [d for d in delta if d is not None]
+        if len(parts) > 2:
+            raise KernelError("add_rmsnorm: at most two deltas")
+        delta = parts[0] if parts else None
+        delta2 = parts[1] if len(parts) > 1 else None
     hidden = weight.numel()
     _need(resid, torch.float32, "residual")
     _need(weight, torch.float32, "norm weight")
@@ -175,6 +213,13 @@ def add_rmsnorm(resid: torch.Tensor, delta: Optional[torch.Tensor], weight: torc
         raise KernelError("add_rmsnorm: residual smaller than the rows asked for")
     if resid.shape[-1] != hidden or out.shape[-1] != hidden or out.numel() < n_rows * hidden:
         raise KernelError("add_rmsnorm: widths differ or output too small")
+    if delta2 is not None:
+        _need(delta2, out.dtype, "second delta")
+        if delta2.shape[-1] != hidden:
+            raise KernelError("add_rmsnorm: delta width differs from the norm's")
+        _check(lib, lib.x0ne_add2_rmsnorm(_ptr(resid), _ptr(delta), _ptr(delta2), _ptr(weight), _ptr(out), dtype_tag(out.dtype),
+                                          _ptr(rows), n_rows, hidden, eps, _stream()), "add_rmsnorm")
+        return
     _check(lib, lib.x0ne_add_rmsnorm(_ptr(resid), _ptr(delta), _ptr(weight), _ptr(out), dtype_tag(out.dtype),
                                      _ptr(rows), n_rows, hidden, eps, _stream()), "add_rmsnorm")
 
@@ -219,19 +264,207 @@ def qk_norm_rope_kv_write(qkv: torch.Tensor, q_norm: Optional[torch.Tensor], k_n
 
 
 def attention_rows(q: torch.Tensor, out: torch.Tensor, cache: PagedCacheArg, row_slot: torch.Tensor,
-                   row_pos: torch.Tensor, n_rows: int, q_heads: int, scale: float, window: int = 0) -> None:
-    """The plain attention kernel: any head size up to 256, any window (0 = none)."""
+                   row_pos: torch.Tensor, n_rows: int, q_heads: int, scale: float, window: int = 0,
+                   extra: Optional[AttnExtraArg] = None) -> None:
+    """The plain attention kernel: keys up to 2,048 wide, values up to 512, any window (0 = none), and
+    what `extra` asks for (see `attn_extra`).  With `extra.q_ld` the queries are rows of a wider buffer."""
     lib = _lib("core")
-    _need(q, q.dtype, "q")
     _need(out, q.dtype, "attention output")
     _need(row_slot, torch.int32, "row slots")
     _need(row_pos, torch.int32, "row positions")
-    width = q_heads * cache.head_dim
-    if q.shape[-1] != width or out.shape[-1] != width or q.numel() < n_rows * width or out.numel() < n_rows * width:
-        raise KernelError("attention: q or output do not match the head counts and rows")
-    _check(lib, lib.x0ne_attention_rows(_ptr(q), _ptr(out), dtype_tag(q.dtype), cache, _ptr(row_slot),
-                                        _ptr(row_pos), n_rows, q_heads, scale, window,
-                                        _stream()), "attention_rows")
+    if not q.is_cuda or (extra is None or not extra.q_ld) and not q.is_contiguous():
+        raise KernelError("attention: q is not a contiguous GPU tensor")
+    vd = extra.v_from_k if extra is not None and extra.v_from_k else cache.value_dim
+    width, out_width = q_heads * cache.head_dim, q_heads * vd
+    if extra is None or not extra.q_ld:
+        if q.shape[-1] != width or q.numel() < n_rows * width:
+            raise KernelError("attention: q does not match the head counts and rows")
+    if out.shape[-1] != out_width or out.numel() < n_rows * out_width:
+        raise KernelError("attention: the output does not match the head counts and rows")
+    if extra is None:
+        _check(lib, lib.x0ne_attention_rows(_ptr(q), _ptr(out), dtype_tag(q.dtype), cache, _ptr(row_slot),
+                                            _ptr(row_pos), n_rows, q_heads, scale, window,
+                                            _stream()), "attention_rows")
+    else:
+        _check(lib, lib.x0ne_attention_rows_ex(_ptr(q), _ptr(out), dtype_tag(q.dtype), cache, _ptr(row_slot),
+                                               _ptr(row_pos), n_rows, q_heads, scale, window, extra,
+                                               _stream()), "attention_rows")
+
+
+def glu_clipped(gate_up: torch.Tensor, out: torch.Tensor, n_rows: int, limit: float, slope: float, shift: float) -> None:
+    """out = g sigmoid(slope g) (u + shift) with g = min(gate, limit), u = clamp(up, -limit, limit), on the
+    packed [gate; up] rows."""
+    lib = _lib("core")
+    _need(gate_up, gate_up.dtype, "gate_up")
+    _need(out, gate_up.dtype, "activation output")
+    inter = out.shape[-1]
+    if gate_up.shape[-1] != 2 * inter or gate_up.numel() < n_rows * 2 * inter or out.numel() < n_rows * inter:
+        raise KernelError("glu_clipped: widths or rows do not match")
+    _check(lib, lib.x0ne_glu_clipped(_ptr(gate_up), _ptr(out), dtype_tag(out.dtype), n_rows, inter, limit, slope, shift,
+                                     _stream()), "glu_clipped")
+
+
+def kv_write_blend(src: torch.Tensor, k_col: int, v_col: int, cache: PagedCacheArg, row_slot: torch.Tensor,
+                   row_pos: torch.Tensor, n_rows: int, mode: int = 0, v_first: Optional[torch.Tensor] = None,
+                   blend: Optional[torch.Tensor] = None) -> None:
+    """Writes the keys (columns from k_col) and values (from v_col) of `src` rows into the cache.  mode 1
+    also keeps the values in `v_first`; mode 2 writes (1 - blend) v + blend v_first, `blend` one float32
+    on the device."""
+    lib = _lib("core")
+    _need(src, src.dtype, "projection rows")
+    _need(row_slot, torch.int32, "row slots")
+    _need(row_pos, torch.int32, "row positions")
+    if src.numel() < n_rows * src.shape[-1] or row_slot.numel() < n_rows or row_pos.numel() < n_rows:
+        raise KernelError("kv_write: buffers smaller than the rows asked for")
+    if v_first is not None:
+        _need(v_first, src.dtype, "first values")
+        if v_first.shape[-1] != cache.kv_heads * cache.value_dim or v_first.numel() < n_rows * v_first.shape[-1]:
+            raise KernelError("kv_write: the buffer of first values does not match the cache's values")
+    if blend is not None:
+        _need(blend, torch.float32, "blend weight")
+    _check(lib, lib.x0ne_kv_write_blend(_ptr(src), dtype_tag(src.dtype), src.shape[-1], k_col, v_col, _ptr(v_first),
+                                        _ptr(blend), mode, cache, _ptr(row_slot), _ptr(row_pos), n_rows, _stream()),
+           "kv_write_blend")
+
+
+def latent_prepare(src: torch.Tensor, dkv_col: int, q_abs: torch.Tensor, norm_w: torch.Tensor, eps: float,
+                   freq: Optional[torch.Tensor], mag: float, table: Optional[torch.Tensor], q_out: torch.Tensor, heads: int,
+                   dim: int, rot: int, rank: int, cache: PagedCacheArg, row_slot: torch.Tensor, row_pos: torch.Tensor,
+                   n_rows: int, write_cache: bool = True) -> None:
+    """Latent attention's rows: normed latent and rotated shared key part into the cache, and the queries
+    [q_abs | rotated part] per head (see mixer_rows.cu).  `q_abs` is [heads, rows, rank]."""
+    lib = _lib("core")
+    _need(src, src.dtype, "projection rows")
+    _need(q_abs, src.dtype, "queries in latent space")
+    _need(q_out, src.dtype, "query output")
+    _need(norm_w, torch.float32, "latent norm weight")
+    _need(row_slot, torch.int32, "row slots")
+    _need(row_pos, torch.int32, "row positions")
+    if q_abs.dim() != 3 or q_abs.shape[0] != heads or q_abs.shape[2] != rank or q_abs.shape[1] < n_rows:
+        raise KernelError("latent_prepare: q_abs is not [heads, rows, rank]")
+    if norm_w.numel() != rank or q_out.shape[-1] != heads * (rank + rot) or q_out.numel() < n_rows * q_out.shape[-1] \
+            or src.numel() < n_rows * src.shape[-1]:
+        raise KernelError("latent_prepare: widths or rows do not match")
+    positions = 0
+    if rot:
+        _need(freq, torch.float32, "rotary frequencies")
+        if freq.numel() * 2 != rot:
+            raise KernelError("latent_prepare: frequencies are not rot / 2")
+        if table is not None:
+            _need(table, torch.float32, "rotary table")
+            if table.dim() != 2 or table.shape[1] != rot:
+                raise KernelError("latent_prepare: the table is not [positions, rot]")
+            positions = table.shape[0]
+    _check(lib, lib.x0ne_latent_prepare(_ptr(src), dtype_tag(src.dtype), src.shape[-1], dkv_col, _ptr(q_abs),
+                                        q_abs.stride(0), _ptr(norm_w), eps, _ptr(freq), mag, _ptr(table), positions,
+                                        _ptr(q_out), heads, dim, rot, rank, cache, _ptr(row_slot), _ptr(row_pos), n_rows,
+                                        1 if write_cache else 0, _stream()), "latent_prepare")
+
+
+def batched_product(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
+    """out[b] = a[b] @ w[b]^T for a [B, M, K], w [B, N, K], out [B, M, N]; `a` and `out` may be strided
+    views (last axis contiguous), `w` is contiguous.  float32: this library's fixed-order FMA kernel, one
+    product per z of the grid; bfloat16: the vendor's strided batched product (float32 accumulation)."""
+    if a.dim() != 3 or w.dim() != 3 or out.dim() != 3 or a.shape[0] != w.shape[0] or a.shape[2] != w.shape[2] \
+            or out.shape != (a.shape[0], a.shape[1], w.shape[1]) or a.stride(2) != 1 or out.stride(2) != 1 or not w.is_contiguous():
+        raise KernelError(f"batched_product: shapes a {tuple(a.shape)} w {tuple(w.shape)} out {tuple(out.shape)}")
+    b, m, k = a.shape
+    n = w.shape[1]
+    if m == 0:
+        return
+    if a.dtype == torch.float32:
+        lib = _lib("core")
+        _check(lib, lib.x0ne_gemm_f32_nt_batched(_ptr(a), _ptr(w), _ptr(out), m, n, k, a.stride(1), k, out.stride(1), b,
+                                                 a.stride(0), n * k, out.stride(0), _stream()), "gemm_f32_nt_batched")
+    elif a.dtype == torch.bfloat16:
+        if out.is_contiguous():
+            torch.bmm(a, w.transpose(1, 2), out=out)
+        else:
+            out.copy_(torch.bmm(a, w.transpose(1, 2)))
+    else:
+        raise KernelError(f"batched_product: no product for {a.dtype}")
+
+
+# ---------------------------------------------------------------------------------------------
+# bfloat16 attention for free key / value widths, masks, sinks and gates (module `flex`)
+# ---------------------------------------------------------------------------------------------
+PREFILL_TILE_ROWS = 128      # rows of a tile of every bfloat16 prefill attention kernel (the pass tables are built with it)
+FLEX_SMEM_LIMIT = 200 * 1024
+
+
+FLEX_VALUE_BUCKETS = (16, 32, 48, 64, 96, 128, 192, 256)     # the value widths the kernels are compiled for
+
+
+def flex_value_bucket(vd: int) -> int:
+    return next((b for b in FLEX_VALUE_BUCKETS if vd <= b), 0)
+
+
+def attention_flex_takes(cache: PagedCacheArg, dtype: torch.dtype, v_from_k: int = 0, decode: bool = False) -> bool:
+    """Whether the general bfloat16 attention kernels take this shape; else the plain kernel does."""
+    if dtype != torch.bfloat16 or cache.page_size != 64:
+        return False
+    vd = v_from_k or cache.value_dim
+    dkp, vdp = -(-cache.head_dim // 16) * 16, flex_value_bucket(vd)
+    if vd <= 0 or vdp == 0:
+        return False
+    ks = (max(dkp, vdp) if v_from_k else dkp) + 8
+    tiles = (64 * ks + (0 if v_from_k else 64 * (vdp + 8))) * 2
+    if decode:
+        smem = 16 * ks * 2 + max(tiles, 4 * 16 * (vdp + 2) * 4)
+    else:
+        smem = 128 * ks * 2 + tiles
+    return smem <= FLEX_SMEM_LIMIT
+
+
+def attention_flex_prefill(q: torch.Tensor, out: torch.Tensor, cache: PagedCacheArg, tile_seq: torch.Tensor,
+                           tile_row0: torch.Tensor, n_tiles: int, seq_first_row: torch.Tensor, seq_slot: torch.Tensor,
+                           seq_pos0: torch.Tensor, q_heads: int, scale: float, window: int, extra: AttnExtraArg) -> None:
+    """Flash attention of a pass whose sequences bring several rows; tiles of up to 128 rows of one sequence."""
+    lib = _lib("flex")
+    _need(out, torch.bfloat16, "attention output")
+    if q.dtype != torch.bfloat16 or not q.is_cuda:
+        raise KernelError("attention_flex: q is not a bfloat16 GPU tensor")
+    for t, what in ((tile_seq, "tile sequences"), (tile_row0, "tile rows"), (seq_first_row, "sequence rows"),
+                    (seq_slot, "sequence slots"), (seq_pos0, "sequence positions")):
+        _need(t, torch.int32, what)
+    if tile_seq.numel() < n_tiles or tile_row0.numel() < n_tiles:
+        raise KernelError("attention_flex: tile tables shorter than the tiles asked for")
+    vd = extra.v_from_k or cache.value_dim
+    if out.shape[-1] != q_heads * vd:
+        raise KernelError("attention_flex: the output width does not match the head counts")
+    for first in range(0, n_tiles, 65535):
+        n = min(65535, n_tiles - first)
+        _check(lib, lib.x0ne_attention_flex_prefill(
+            _ptr(q), _ptr(out), cache, tile_seq.data_ptr() + 4 * first, tile_row0.data_ptr() + 4 * first, n,
+            _ptr(seq_first_row), _ptr(seq_slot), _ptr(seq_pos0), q_heads, scale, window, extra, _stream()),
+            "attention_flex_prefill")
+
+
+def attention_flex_scratch_bytes(n_rows: int, q_heads: int, kv_heads: int, vd: int, splits: int) -> int:
+    chunks, vdp = -(-(q_heads // kv_heads) // 16), flex_value_bucket(vd)
+    return n_rows * kv_heads * chunks * splits * 16 * (vdp + 2) * 4 if splits > 1 else 0
+
+
+def attention_flex_decode(q: torch.Tensor, out: torch.Tensor, cache: PagedCacheArg, row_slot: torch.Tensor,
+                          row_pos: torch.Tensor, n_rows: int, q_heads: int, scale: float, window: int,
+                          extra: AttnExtraArg, splits: int = 1, scratch: Optional[torch.Tensor] = None) -> None:
+    """One query row per sequence; `splits` blocks share a row's pages and meet in `scratch`."""
+    lib = _lib("flex")
+    _need(out, torch.bfloat16, "attention output")
+    if q.dtype != torch.bfloat16 or not q.is_cuda:
+        raise KernelError("attention_flex: q is not a bfloat16 GPU tensor")
+    _need(row_slot, torch.int32, "row slots")
+    _need(row_pos, torch.int32, "row positions")
+    vd = extra.v_from_k or cache.value_dim
+    if out.shape[-1] != q_heads * vd or out.numel() < n_rows * q_heads * vd or row_slot.numel() < n_rows or row_pos.numel() < n_rows:
+        raise KernelError("attention_flex: output or row tables do not match the rows asked for")
+    nbytes = scratch.numel() * scratch.element_size() if scratch is not None else 0
+    _check(lib, lib.x0ne_attention_flex_decode(_ptr(q), _ptr(out), cache, _ptr(row_slot), _ptr(row_pos), n_rows, q_heads,
+                                               scale, window, extra, splits, _ptr(scratch), nbytes, _stream()),
+           "attention_flex_decode")
+    if splits > 1:
+        global LAUNCHES
+        LAUNCHES += 1
 
 
 def swiglu(gate_up: torch.Tensor, out: torch.Tensor, n_rows: int) -> None:
@@ -306,7 +539,7 @@ def sample(logits: torch.Tensor, n_rows: int, out_token: torch.Tensor, *, temper
 def fast_attention_takes(cache: PagedCacheArg, dtype: torch.dtype) -> bool:
     """Whether the tensor-core attention kernels take this shape; otherwise the plain kernel does."""
     return dtype == torch.bfloat16 and cache.page_size == 64 and cache.head_dim % 16 == 0 \
-        and 16 <= cache.head_dim <= 128
+        and 16 <= cache.head_dim <= 128 and cache.v_dim == 0
 
 
 def attention_prefill_bf16(q: torch.Tensor, out: torch.Tensor, cache: PagedCacheArg, tile_seq: torch.Tensor,
@@ -552,7 +785,7 @@ def gemm_bf16_skinny_tcgen05(x: torch.Tensor, w: torch.Tensor, y: torch.Tensor, 
 
 def attention_tc_takes(cache: PagedCacheArg, dtype: torch.dtype) -> bool:
     """Whether the tcgen05 prefill attention takes this shape."""
-    return dtype == torch.bfloat16 and cache.page_size == 64 and cache.head_dim in (64, 128)
+    return dtype == torch.bfloat16 and cache.page_size == 64 and cache.head_dim in (64, 128) and cache.v_dim == 0
 
 
 def attention_prefill_tcgen05(q: torch.Tensor, out: torch.Tensor, cache: PagedCacheArg, tile_seq: torch.Tensor,

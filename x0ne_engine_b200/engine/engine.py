@@ -122,7 +122,7 @@ class Engine:
         self.pass_graph_replays = 0
         if self.dtype == torch.bfloat16:
             from ..csrc import ops
-            self._tile_rows = ops.attention_prefill_tile_rows()
+            self._tile_rows = ops.PREFILL_TILE_ROWS      # (a constant, so that no kernel library is built for it)
         else:
             self._tile_rows = 64
 

@@ -84,7 +84,7 @@ def step_bytes_of_spec(spec: ModelSpec, dtype_bytes: int = 2):
         weights += sum(nbytes(n) for _, cls, ps in layer_part_classes(layer) for n in cls.tensor_needs(ps))
         need = cache_need_of_layer(layer)
         if need.kind == "kv" and e.reads_cache_of is None:
-            cache += 2 * need.kv_heads * need.head_dim * dtype_bytes
+            cache += need.kv_heads * (need.head_dim + (need.head_dim if need.v_dim is None else need.v_dim)) * dtype_bytes
     return weights, cache
 
 

@@ -87,7 +87,7 @@ def main(argv=None) -> int:
 
     os.makedirs(args.out, exist_ok=True)
     capacity = pages_for(args.max_tokens, PAGE_SIZE) * PAGE_SIZE
-    engine = Engine.from_folder(args.model, dtype=args.dtype, device=args.device, max_tokens=capacity,
+    engine = Engine.from_folder(args.model, dtype=args.dtype, device=args.device, max_tokens=capacity, max_seq_len=capacity,
                                 max_step_tokens=args.max_step_tokens or min(capacity, 4096))
     print(f"[x0ne-b200] trace_run: {engine.describe()}", file=sys.stderr, flush=True)
     head = {"schema": 1, "model": os.path.abspath(args.model), "architecture": engine.spec.architecture,

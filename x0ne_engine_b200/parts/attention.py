@@ -34,6 +34,35 @@ def run_attention(ctx, q, out, view, n_rows, q_heads, scale, window):
                q_heads, scale, window)
 
 
+def flex_decode_splits(ctx, n_rows: int, kv_heads: int, q_heads: int, visible: int) -> int:
+    """Blocks per (sequence, kv head, 16 q heads) of a decode pass of the general kernel: enough to
+    put two blocks on every multiprocessor, each with at least two pages of the at most `visible`
+    keys a row reads.  Depends on the pass's numbers only, so a replayed graph keeps it."""
+    units = max(1, n_rows * kv_heads * -(-(q_heads // kv_heads) // 16))
+    pages = -(-max(1, visible) // 64) + 1
+    return max(1, min(2 * max(1, ctx.sm_count) // units, pages // 2, 32))
+
+
+def run_attention_ex(ctx, q, out, view, n_rows, q_heads, scale, window, extra):
+    """Attention with what `extra` asks for (`ops.attn_extra`: chunked mask, values out of the keys,
+    sink, gate, queries inside a wider buffer): the general bfloat16 kernels where they take the
+    shape, else the plain kernel (which is also the whole 32-bit path)."""
+    if not ops.attention_flex_takes(view, q.dtype, extra.v_from_k, ctx.decode):
+        ops.attention_rows(q, out, view, ctx.row_slot, ctx.row_pos, n_rows, q_heads, scale, window, extra)
+    elif ctx.decode:
+        visible = min(v for v in (ctx.max_context, extra.chunk, window) if v)
+        splits = flex_decode_splits(ctx, n_rows, view.kv_heads, q_heads, visible)
+        scratch = None
+        if splits > 1:
+            vd = extra.v_from_k or view.value_dim
+            scratch = ctx.ws.buffer("attn.flex_parts", (ops.attention_flex_scratch_bytes(ctx.ws.max_rows, q_heads, view.kv_heads, vd, 32) // 4,),
+                                    torch.float32)
+        ops.attention_flex_decode(q, out, view, ctx.row_slot, ctx.row_pos, n_rows, q_heads, scale, window, extra, splits, scratch)
+    else:
+        ops.attention_flex_prefill(q, out, view, ctx.tile_seq, ctx.tile_row0, ctx.n_tiles, ctx.seq_first_row, ctx.seq_slot,
+                                   ctx.seq_pos0, q_heads, scale, window, extra)
+
+
 # what a decode attention block costs besides walking its pages (table look-ups, first slice, merges),
 # in pages' worth of time: about 3 us against 0.3 us per page of 64 keys x 128 values, measured at 8 kv heads;
 # the split only has to be near the best one, and the same rule chose well at 1 to 256 sequences and

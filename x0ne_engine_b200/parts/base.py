@@ -5,7 +5,8 @@ A part is built from a `PartSpec` (its sizes, constants and checkpoint tensor na
 sees the model's name or its config.json.  The kinds:
 
   * `Norm`         — `add_norm(ctx, resid, delta, out, n_rows, rows=None)`: adds `delta` (may be
-                     None) into the float32 residual and writes the normed rows.
+                     None, or a pair of tensors whose float32 sum is added: the two branches of
+                     a parallel arrangement) into the float32 residual and writes the normed rows.
   * `Mixer`        — mixes information between the positions of a sequence.  Says what it keeps
                      per sequence with `cache_need(spec)`; `forward(ctx, entry, x, n_rows)` reads
                      and writes that through `ctx.cache` for run-order entry `entry` and returns
@@ -41,7 +42,8 @@ class CacheNeed:
     """What a mixer keeps for each sequence.
 
     kind "kv": keys and values of `kv_heads` x `head_dim` per position; all positions, or the
-    last `window` of them.  kind "state": a float32 array of `state_shape` per sequence, zero
+    last `window` of them.  `v_dim` is the width of a value row where it differs from the keys'
+    (None: the same; 0: no values are kept, the mixer reads them out of its keys).  kind "state": a float32 array of `state_shape` per sequence, zero
     when the sequence starts.  kind "none": nothing.
     """
     kind: str = "none"
@@ -49,6 +51,7 @@ class CacheNeed:
     head_dim: int = 0
     window: Optional[int] = None
     state_shape: Tuple[int, ...] = ()
+    v_dim: Optional[int] = None
 
 
 @dataclass
@@ -101,6 +104,9 @@ class Mixer(Part):
 
 
 class FeedForward(Part):
+    out_buffer = "delta"        # the workspace buffer the result goes to; an arrangement that runs the
+                                # feed-forward beside the mixer names another one
+
     def forward(self, ctx, x: torch.Tensor, n_rows: int) -> torch.Tensor:
         raise NotImplementedError
 

@@ -19,4 +19,27 @@ class PreNormBlock(Block):
         return self.ffn.forward(ctx, normed, ctx.n_rows)
 
 
+class ParallelBlock(Block):
+    """x += mixer(norm(x)) + ffn(norm(x)): one norm, both branches read its output, and their results
+    are summed in float32 as they are added to the residual.  The add is again fused into the next
+    norm, so the block hands on both results as a pair.  A layer may leave the feed-forward out."""
+    replayable = True
+    ROLES = {"norm": "norm", "mixer": "mixer", "ffn": "feed_forward"}
+    OPTIONAL = ("ffn",)
+
+    def __init__(self, parts):
+        super().__init__(parts)
+        if self.ffn is not None:
+            self.ffn.out_buffer = "ffn.delta"       # beside the mixer's result, not over it
+
+    def forward(self, ctx, entry, resid, delta, cache_entry=None, write_cache=True):
+        normed = ctx.ws.buffer("normed", (ctx.ws.max_rows, resid.shape[-1]), ctx.dtype)
+        self.norm.add_norm(ctx, resid, delta, normed, ctx.n_rows)
+        mixed = self.mixer.forward(ctx, entry, normed, ctx.n_rows, cache_entry=cache_entry, write_cache=write_cache)
+        if self.ffn is None:
+            return mixed
+        return (mixed, self.ffn.forward(ctx, normed, ctx.n_rows))
+
+
 BLOCKS.register("prenorm", PreNormBlock)
+BLOCKS.register("parallel", ParallelBlock)

@@ -42,7 +42,7 @@ class SwiGLU(FeedForward):
     def forward(self, ctx, x, n_rows):
         gu = ctx.ws.buffer("ffn.gate_up", (ctx.ws.max_rows, 2 * self.inter), self.env.dtype)
         act = ctx.ws.buffer("ffn.act", (ctx.ws.max_rows, self.inter), self.env.dtype)
-        out = ctx.ws.buffer("delta", (ctx.ws.max_rows, self.hidden), self.env.dtype)
+        out = ctx.ws.buffer(self.out_buffer, (ctx.ws.max_rows, self.hidden), self.env.dtype)
         kernel = ops.product_kernel(self.gate_up.weight, n_rows, fused=True)       # the routing table (csrc/routes.py)
         if kernel == "skinny":
             ops.gemm_bf16_skinny_tcgen05(x, self.gate_up.weight, act, n_rows, swiglu=True)   # 9 to 64 rows, tcgen05
@@ -57,4 +57,28 @@ class SwiGLU(FeedForward):
         return out
 
 
+class ClippedGLU(SwiGLU):
+    """down( g sigmoid(slope g) (u + shift) ) with g = min(gate x, limit) and u = clamp(up x, -limit,
+    limit): a gated unit whose gate is bounded above and whose linear branch is bounded on both sides
+    and shifted.  One product on the packed [gate; up] weight, the activation in float32, one product
+    with down.  Parameters: hidden_size, intermediate_size, limit, slope, shift, names.{gate, up, down}."""
+    replayable = True
+
+    def __init__(self, spec, env):
+        super().__init__(spec, env)
+        self.limit = float(spec["limit"])
+        self.slope = float(spec.get("slope", 1.0))
+        self.shift = float(spec.get("shift", 0.0))
+
+    def forward(self, ctx, x, n_rows):
+        gu = ctx.ws.buffer("ffn.gate_up", (ctx.ws.max_rows, 2 * self.inter), self.env.dtype)
+        act = ctx.ws.buffer("ffn.act", (ctx.ws.max_rows, self.inter), self.env.dtype)
+        out = ctx.ws.buffer(self.out_buffer, (ctx.ws.max_rows, self.hidden), self.env.dtype)
+        self.gate_up(x, gu, n_rows)
+        ops.glu_clipped(gu, act, n_rows, self.limit, self.slope, self.shift)
+        self.down(act, out, n_rows)
+        return out
+
+
 FEED_FORWARDS.register("swiglu", SwiGLU)
+FEED_FORWARDS.register("clipped_glu", ClippedGLU)

@@ -1,6 +1,8 @@
 """Rotary position encoding: the table of inverse frequencies."""
 from __future__ import annotations
 
+import math
+
 import numpy as np
 import torch
 
@@ -49,6 +51,67 @@ class Rope(PositionEncoding):
         return self._cos_sin
 
 
+def yarn_frequencies(rotary_dim: int, theta: float, scaling) -> tuple:
+    """(frequency per pair as float64 [rotary_dim / 2], factor on cos and sin).
+
+    Plain frequencies are f_i = theta^(-2i / rotary_dim).  With `scaling` = {factor, original, fast,
+    slow} (YaRN): the pair index at which a wave makes t turns over `original` positions is
+    idx(t) = rotary_dim ln(original / (2 pi t)) / (2 ln theta); pairs below lo = max(floor(idx(fast)), 0)
+    keep f_i, pairs above hi = min(ceil(idx(slow)), rotary_dim - 1) get f_i / factor, and between them
+    the two are blended linearly; cos and sin are multiplied by 0.1 ln(factor) + 1."""
+    i = np.arange(rotary_dim // 2, dtype=np.float64)
+    f = np.power(float(theta), -2.0 * i / rotary_dim)
+    if not scaling:
+        return f, 1.0
+    factor, original = float(scaling["factor"]), float(scaling["original"])
+
+    def idx(turns: float) -> float:
+        return rotary_dim * math.log(original / (2.0 * math.pi * turns)) / (2.0 * math.log(float(theta)))
+
+    lo = max(math.floor(idx(float(scaling["fast"]))), 0)
+    hi = min(math.ceil(idx(float(scaling["slow"]))), rotary_dim - 1)
+    ramp = np.clip((i - lo) / max(hi - lo, 0.001), 0.0, 1.0)
+    return f / factor * ramp + f * (1.0 - ramp), 0.1 * math.log(factor) + 1.0
+
+
+class YarnRope(PositionEncoding):
+    """Rotary encoding over `rotary_dim` values with YaRN-scaled frequencies.  `layout` says which
+    values pair up: "interleaved" turns value 2i with value 2i + 1, "half" value i with value
+    i + rotary_dim / 2.  The pair (u, v) at position p becomes (u c - v s, v c + u s) with
+    c = mag cos(p f_i), s = mag sin(p f_i).  The rotation runs inside the mixer's kernel; this part
+    owns the frequencies and the table.  Parameters: rotary_dim, theta, scaling (None or {factor,
+    original, fast, slow}), layout."""
+    replayable = True
+    TABLE_POSITIONS = 1 << 16      # the table covers this many positions at most; kernels compute the rest
+
+    def __init__(self, spec, env):
+        super().__init__(spec, env)
+        self.rotary_dim = int(spec["rotary_dim"])
+        if self.rotary_dim % 2 or self.rotary_dim <= 0:
+            raise ValueError(f"rotary_dim {self.rotary_dim} must be even and positive")
+        self.theta = float(spec["theta"])
+        self.layout = spec.get("layout", "interleaved")
+        if self.layout not in ("interleaved", "half"):
+            raise ValueError(f"rotary layout {self.layout!r} is neither 'interleaved' nor 'half'")
+        self.freq64, self.mag = yarn_frequencies(self.rotary_dim, self.theta, spec.get("scaling"))
+        self.inv_freq = self.freq64.astype(np.float32)
+        self.table = torch.from_numpy(self.inv_freq).to(env.device)
+        self._cos_sin = None
+
+    def rotary(self):
+        return self.table, self.rotary_dim
+
+    def cos_sin_table(self, positions: int):
+        """float32 [positions, rotary_dim]: mag cos then mag sin of position x frequency, the angle taken
+        in float64 on the host."""
+        positions = max(1, min(int(positions), self.TABLE_POSITIONS))
+        if self._cos_sin is None or self._cos_sin.shape[0] < positions:
+            ang = np.arange(positions, dtype=np.float64)[:, None] * self.freq64[None, :]
+            tab = (np.concatenate([np.cos(ang), np.sin(ang)], axis=1) * self.mag).astype(np.float32)
+            self._cos_sin = torch.from_numpy(tab).to(self.env.device)
+        return self._cos_sin
+
+
 class NoPosition(PositionEncoding):
     """No position encoding: mixers leave q and k unrotated."""
     replayable = True
@@ -56,3 +119,4 @@ class NoPosition(PositionEncoding):
 
 POSITIONS.register("rope", Rope)
 POSITIONS.register("none", NoPosition)
+POSITIONS.register("yarn_rope", YarnRope)
