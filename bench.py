@@ -131,6 +131,110 @@ def synthetic_ids(n, vocab, seed):
     return out
 
 
+# ---------------------------------------------------------------------------------------------
+# --design rovurax: the Rovurax design beside the Qwen3 design at equal sizes
+# ---------------------------------------------------------------------------------------------
+DESIGN_SIZES = {
+    # width, feed-forward, q heads, kv heads, head size, latent rank, rotated part: the layer sizes of a 1.7B and of an 8B model
+    "1.7b": dict(width=2048, ff=6144, heads=16, kv_heads=8, dim=128, kv_rank=256, rot_dim=64),
+    "8b": dict(width=4096, ff=12288, heads=32, kv_heads=8, dim=128, kv_rank=256, rot_dim=64),
+}
+
+
+def design_configs(size: dict, layers: int, vocab: int, chunk: int):
+    """(Rovurax configuration, Qwen3 configuration) with the same width, heads, feed-forward, depth and
+    vocabulary.  Of every four Rovurax layers three are chunk-masked attention with blended values and
+    one is latent attention with YaRN-scaled rotation, a sink and a gate."""
+    import x0ne_engine_b200 as x
+    from x0ne_engine_b200.config import config_from_dict
+    w, ff, H, G, d = size["width"], size["ff"], size["heads"], size["kv_heads"], size["dim"]
+    mlp = {"ff": ff, "kind": "dense", "limit": 7.0}
+    att = {"type": "attention", "mlp": mlp, "mixer": {"dim": d, "heads": H, "kv_heads": G, "vdim": d, "scale": d ** -0.5,
+                                                        "mask": {"size": chunk}, "v_mix": True}}
+    lat = {"type": "latent_attention", "mlp": mlp, "mixer": {
+        "dim": d, "heads": H, "kv_rank": size["kv_rank"], "rot_dim": size["rot_dim"], "vdim": d, "scale": (d + size["rot_dim"]) ** -0.5,
+        "rot": {"base": 1000000.0, "dims": size["rot_dim"], "scaling": {"factor": 4.0, "original": 4096, "fast": 32.0, "slow": 1.0}}}}
+    new = config_from_dict({"architecture": "Rovurax", "vocab": vocab, "width": w, "norm": {"eps": 1e-6},
+                            "layers": [lat if i % 4 == 3 else att for i in range(layers)]})
+    old = x.Qwen3Config(hidden_size=w, intermediate_size=ff, num_hidden_layers=layers, num_attention_heads=H,
+                        num_key_value_heads=G, head_dim=d, vocab_size=vocab, max_position_embeddings=40960,
+                        rms_norm_eps=1e-6, rope_theta=1000000.0, tie_word_embeddings=False, dtype="bfloat16")
+    return new, old
+
+
+def design_bench(args) -> int:
+    """Prefill and decode throughput of Rovurax and of Qwen3 at equal sizes, random bfloat16 weights, through the same
+    engine, step function and decode graphs.  One JSON line."""
+    import torch
+
+    import x0ne_engine_b200 as x
+    from x0ne_engine_b200.engine.decode import DeviceBatch
+    from x0ne_engine_b200.engine.generate import Row
+    from x0ne_engine_b200.sampling import SamplingParams
+    pk = peaks()
+    K, W, B, T = args.steps, max(args.warmup, 8), args.batch, args.prefill_tokens
+    ctx = T + K + W + 64
+    layers = args.layers or 8
+    vocab = 32768
+    rows_out = []
+    for name in args.sizes.split(","):
+        size = DESIGN_SIZES[name]
+        for design, cfg in zip(("rovurax", "qwen3"), design_configs(size, layers, vocab, args.chunk)):
+            model = x.Model.random(cfg, seed=0, dtype="bfloat16", max_batch=B, max_ctx=ctx, max_step_tokens=max(T, 64))
+            eng = model.engine
+            ids = synthetic_ids(T, vocab, 20261104)
+            times = []
+            for i in range(W + 3):
+                slot = eng.new_sequence(T)
+                s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                torch.cuda.synchronize()
+                s.record()
+                eng.step([slot], [ids])
+                e.record()
+                torch.cuda.synchronize()
+                if i >= W:
+                    times.append(s.elapsed_time(e))
+                eng.free_sequence(slot)
+            pre_ms = statistics.median(times)
+            rows = [Row(i, synthetic_ids(T, vocab, 0x0C0E5EED + i), SamplingParams(max_tokens=ctx), ctx - T, i) for i in range(B)]
+            runner = DeviceBatch(eng, B, cuda_graph=True)
+            runner.run_ahead = False
+            try:
+                runner.start(rows)
+                live = list(range(B))
+                for _ in range(W):
+                    runner.step(live)
+                g = runner.last_graph
+                s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                torch.cuda.synchronize()
+                s.record()
+                for _ in range(K):
+                    g.replay()
+                e.record()
+                torch.cuda.synchronize()
+                dec_ms = s.elapsed_time(e) / K
+                for sl in runner.slots:
+                    eng.cache.lengths[sl] += K
+                launches = runner.launches_per_step
+            finally:
+                runner.close()
+            weight_bytes, kv_per_tok = eng.model.step_weight_bytes(), eng.cache.bytes_per_token()
+            step_bytes = weight_bytes + B * (T + W + K / 2.0) * kv_per_tok
+            rows_out.append({"size": name, "design": design, "layers": layers, "prefill_tokens": T, "prefill_ms": pre_ms,
+                             "prefill_tok_s": T / (pre_ms / 1e3), "decode_batch": B, "decode_ms_per_step": dec_ms,
+                             "decode_tok_s": B / (dec_ms / 1e3), "decode_bytes_per_step": step_bytes,
+                             "decode_frac_of_hbm": step_bytes / (dec_ms / 1e3) / 1e9 / pk["hbm_gbs"],
+                             "launches_per_decode_step": launches, "cache_bytes_per_token": kv_per_tok})
+            print(f"[bench] {name} {design}: prefill {T} tokens {pre_ms:.2f} ms, decode b{B} {dec_ms:.3f} ms/step "
+                  f"({rows_out[-1]['decode_frac_of_hbm']:.2f} of {pk['source']} copy bandwidth)", file=sys.stderr, flush=True)
+            del runner, model, eng
+            torch.cuda.empty_cache()
+    print(json.dumps({"metric": "prefill and decode tokens/s of Rovurax beside Qwen3 at equal sizes (random bf16 weights)",
+                      "unit": "tokens/s", "n_gpus": 1, "steps": K, "warmup": W, "dtype": "bf16", "data": "synthetic",
+                      "impl": "ours", "chunk": args.chunk, "peaks": pk, "rows": rows_out}))
+    return 0
+
+
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -143,7 +247,13 @@ def main() -> int:
     ap.add_argument("--prefill-tokens", type=int, default=2048)
     ap.add_argument("--no-points", action="store_true", help="skip decode at batch 1 and 64")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--design", default=None, choices=["rovurax"],
+                    help="instead of the default workload: this design beside Qwen3 at equal sizes (prefill and decode)")
+    ap.add_argument("--sizes", default="1.7b,8b", help="with --design: which of " + ", ".join(DESIGN_SIZES))
+    ap.add_argument("--chunk", type=int, default=1024, help="with --design: positions per chunk of the masked attention")
     args = ap.parse_args()
+    if args.design is not None and args.impl == "ours" and args.gpus == 1:
+        return design_bench(args)
 
     if args.impl == "reference":
         print(json.dumps({"impl": "reference", "unavailable":

@@ -76,16 +76,16 @@ def make_tensors(cfg: dict, seed: int, sharp: float = 1.0):
         t[p + "norm1"] = vec(w)
         if layer["type"] == "attention":
             H, G, d, dv = m["heads"], m["kv_heads"], m["dim"], m["vdim"]
-            t[p + "mix.q"] = mat(H * d, w, 2.0 * sharp)
-            t[p + "mix.k"] = mat(G * d, w, 2.0)
+            t[p + "mix.q"] = mat(H * d, w, 1.4 * sharp)
+            t[p + "mix.k"] = mat(G * d, w, 1.4)
             t[p + "mix.v"] = mat(G * dv, w)
             t[p + "mix.o"] = mat(w, H * dv)
             if m.get("v_mix"):
                 t[p + "mix.vmix"] = (0.25 + 0.5 * torch.rand((), generator=g)).bfloat16().float()
         else:
             H, d, r, dv, rank = m["heads"], m["dim"], m["rot_dim"], m["vdim"], m["kv_rank"]
-            t[p + "mix.q"] = mat(H * (d + r), w, 2.0 * sharp)
-            t[p + "mix.dkv"] = mat(rank + r, w, 2.0)
+            t[p + "mix.q"] = mat(H * (d + r), w, 1.4 * sharp)
+            t[p + "mix.dkv"] = mat(rank + r, w, 1.4)
             t[p + "mix.dkv.norm"] = vec(rank)
             t[p + "mix.uk"] = mat(H * d, rank)
             t[p + "mix.uv"] = mat(H * dv, rank)
@@ -94,8 +94,8 @@ def make_tensors(cfg: dict, seed: int, sharp: float = 1.0):
             t[p + "mix.o"] = mat(w, H * dv)
         if layer.get("mlp"):
             ff = layer["mlp"]["ff"]
-            t[p + "mlp.gate"] = mat(ff, w, 2.0)
-            t[p + "mlp.up"] = mat(ff, w, 2.0)
+            t[p + "mlp.gate"] = mat(ff, w, 1.2)
+            t[p + "mlp.up"] = mat(ff, w, 1.2)
             t[p + "mlp.down"] = mat(w, ff)
     t["final.norm"] = vec(w)
     t["head"] = mat(cfg["vocab"], w)

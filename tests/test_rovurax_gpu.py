@@ -412,3 +412,31 @@ def test_attention_on_a_ring_that_has_lapped():
     ops.attention_flex_decode(q, out, view, slots, pos, 2, H_, 0.3, window, ops.attn_extra(), 2,
                               torch.empty(ops.attention_flex_scratch_bytes(2, H_, G, dv, 2) // 4, dtype=torch.float32, device=DEV))
     assert (out.float() - want).abs().max() <= 2 ** -7 * want.abs().max()
+
+
+@pytest.mark.parametrize("rows,inter,k", [(3, 96, 64), (8, 200, 72), (16, 256, 128), (40, 512, 256), (800, 384, 128)])
+def test_clipped_unit_in_the_products_epilogues(rows, inter, k):
+    """The gate|up product with the clipped unit in its epilogue (every kernel that takes the shape)
+    against the product in float64 followed by the plain formula."""
+    from x0ne_engine_b200.csrc import ops
+    g = torch.Generator().manual_seed(rows)
+    limit, slope, shift = 0.8, 1.702, 1.0
+    x = torch.randn(rows, k, generator=g).bfloat16().to(DEV)
+    w = (torch.randn(2 * inter, k, generator=g) * (2.0 / k ** 0.5)).bfloat16().to(DEV)
+    gu = x.double() @ w.double().T
+    gate, up = gu[:, :inter].clamp(max=limit), gu[:, inter:].clamp(-limit, limit)
+    want = gate * torch.sigmoid(slope * gate) * (up + shift)
+    assert (gu[:, :inter] > limit).any() and (gu[:, inter:].abs() > limit).any()
+    ran = 0
+    for name, takes, fn in [("smallm", ops.gemm_smallm_takes(w, rows, True), ops.gemm_bf16_smallm),
+                            ("skinny", ops.gemm_skinny_tc_takes(w, rows), ops.gemm_bf16_skinny_tcgen05),
+                            ("tc", ops.gemm_tc_takes(w, rows) and rows >= 128, ops.gemm_bf16_tcgen05)]:
+        if not takes:
+            continue
+        y = torch.zeros((rows, inter), dtype=torch.bfloat16, device=DEV)
+        fn(x, w, y, rows, swiglu=True, glu=(limit, slope, shift))
+        ops.check_tc_status(torch.device(DEV))
+        err = (y.double() - want).abs().max().item()
+        assert err <= 2 ** -7 * want.abs().max().item(), f"{name}: {err}"
+        ran += 1
+    assert ran >= 1

@@ -25,6 +25,7 @@ Commands and their options follow the reference's own programs where it has them
       with the time from the end of the kernel before it to its own end (what it adds to the step)
       and its own duration, summed per kernel and listed for one layer in the middle of the model
   kernel-bench --kernel NAME [sizes] [--impl ours|reference]   times one kernel alone with CUDA events
+      (attention_flex_prefill / attention_flex_decode take --v-dim, --chunk and --latent-rank)
       (the reference's per-kernel timing entry: x0ne-core/runtime/src/ops.rs:579-681).  With
       `--impl reference` the reference project's own kernel of that name (attention_decode,
       attention_prefill, add_rmsnorm, qk_norm_rope, swiglu), compiled unchanged from its sources, runs
@@ -442,6 +443,64 @@ def cmd_kernel_bench(a) -> int:
         timed(fn, 2 * T * qh * hd * 2 + 2 * T * kvh * hd * 2, 4.0 * qh * hd * T * (T + 1) / 2)
         return 0
 
+    if a.kernel in ("attention_flex_prefill", "attention_flex_decode"):
+        # the general kernels; --v-dim, --chunk and --latent-rank (values out of the keys, one kv head's row read by all heads)
+        from .parts.attention import flex_decode_splits
+        hd, kvh, qh = a.head_dim, a.kv_heads, a.q_heads
+        rank = a.latent_rank
+        vd = 0 if rank else (a.v_dim or hd)
+        out_vd = rank or vd
+        decode = a.kernel.endswith("decode")
+        B, T = (a.batch, a.context) if decode else (1, a.context)
+        pages_per = (T + 63) // 64
+        page_elems = kvh * 64 * (hd + vd)
+        kv_bytes = B * pages_per * page_elems * 2
+        copies = max(2, int(math.ceil(256e6 / kv_bytes)) + 1) if decode else 1
+        n_pages = B * pages_per
+        stores = [torch.randn(n_pages, page_elems, device=dev).bfloat16() for _ in range(copies)]
+        table = torch.arange(n_pages, dtype=torch.int32, device=dev).reshape(B, pages_per).contiguous()
+        v_tag = -1 if rank else (0 if vd == hd else vd)
+        views = [ops.PagedCacheArg(s.data_ptr(), table.data_ptr(), page_elems, pages_per, pages_per, 64, kvh, hd, n_pages, v_tag)
+                 for s in stores]
+        extra = ops.attn_extra(chunk=a.chunk, v_from_k=rank)
+        visible = min(T, a.chunk) if a.chunk else T
+        mk = lambda v: torch.tensor(v, dtype=torch.int32, device=dev)   # noqa: E731
+        i = [0]
+        if decode:
+            q = torch.randn(B, qh * hd, device=dev).bfloat16()
+            out = torch.empty(B, qh * out_vd, device=dev, dtype=torch.bfloat16)
+            slots, pos = torch.arange(B, dtype=torch.int32, device=dev), torch.full((B,), T - 1, dtype=torch.int32, device=dev)
+
+            class Ctx:
+                sm_count = torch.cuda.get_device_properties(0).multi_processor_count
+            splits = a.splits or flex_decode_splits(Ctx, B, kvh, qh, visible)
+            scratch = torch.empty(max(1, ops.attention_flex_scratch_bytes(B, qh, kvh, out_vd, splits) // 4), device=dev)
+
+            def fn():
+                v = views[i[0] % copies]
+                i[0] += 1
+                ops.attention_flex_decode(q, out, v, slots, pos, B, qh, 1 / math.sqrt(hd), 0, extra, splits, scratch)
+            print(f"splits {splits}", file=sys.stderr)
+            timed(fn, B * visible * kvh * (hd + vd) * 2, 2.0 * B * qh * (hd + out_vd) * visible)
+        else:
+            q = torch.randn(T, qh * hd, device=dev).bfloat16()
+            out = torch.empty(T, qh * out_vd, device=dev, dtype=torch.bfloat16)
+            tr = ops.PREFILL_TILE_ROWS
+            n_tiles = (T + tr - 1) // tr
+            tile_seq, tile_row0 = mk([0] * n_tiles), mk(list(range(0, T, tr)))
+            first, sslot, spos0 = mk([0, T]), mk([0]), mk([0])
+            pairs = sum(min(p % a.chunk, p) + 1 if a.chunk else p + 1 for p in range(T))      # (query, key) pairs a row may see
+            timed(lambda: ops.attention_flex_prefill(q, out, views[0], tile_seq, tile_row0, n_tiles, first, sslot, spos0, qh,
+                                                     1 / math.sqrt(hd), 0, extra),
+                  T * qh * (hd + out_vd) * 2 + T * kvh * (hd + vd) * 2, 2.0 * qh * (hd + out_vd) * pairs)
+        return 0
+    if a.kernel == "glu_clipped":
+        rows, inter = a.m, a.n
+        gu = torch.randn(rows, 2 * inter, device=dev).bfloat16()
+        out = torch.empty(rows, inter, device=dev, dtype=torch.bfloat16)
+        copies = 1
+        timed(lambda: ops.glu_clipped(gu, out, rows, 7.0, 1.702, 1.0), rows * inter * 6)
+        return 0
     if a.kernel == "add_rmsnorm":
         rows, h = a.m, a.n
         resid = torch.randn(rows, h, device=dev)
@@ -556,6 +615,64 @@ def _kernel_bench_reference(a, timed) -> int:
         timed(lambda: R.attention_prefill(k, q, kc, vc, out, pos0, T, qh, kvh, T, 1 / math.sqrt(hd)),
               2 * T * qh * hd * 2 + 2 * T * kvh * hd * 2, 4.0 * qh * hd * T * (T + 1) / 2, 1)
         return 0
+    if a.kernel in ("attention_flex_prefill", "attention_flex_decode"):
+        # the general kernels; --v-dim, --chunk and --latent-rank (values out of the keys, one kv head's row read by all heads)
+        from .parts.attention import flex_decode_splits
+        hd, kvh, qh = a.head_dim, a.kv_heads, a.q_heads
+        rank = a.latent_rank
+        vd = 0 if rank else (a.v_dim or hd)
+        out_vd = rank or vd
+        decode = a.kernel.endswith("decode")
+        B, T = (a.batch, a.context) if decode else (1, a.context)
+        pages_per = (T + 63) // 64
+        page_elems = kvh * 64 * (hd + vd)
+        kv_bytes = B * pages_per * page_elems * 2
+        copies = max(2, int(math.ceil(256e6 / kv_bytes)) + 1) if decode else 1
+        n_pages = B * pages_per
+        stores = [torch.randn(n_pages, page_elems, device=dev).bfloat16() for _ in range(copies)]
+        table = torch.arange(n_pages, dtype=torch.int32, device=dev).reshape(B, pages_per).contiguous()
+        v_tag = -1 if rank else (0 if vd == hd else vd)
+        views = [ops.PagedCacheArg(s.data_ptr(), table.data_ptr(), page_elems, pages_per, pages_per, 64, kvh, hd, n_pages, v_tag)
+                 for s in stores]
+        extra = ops.attn_extra(chunk=a.chunk, v_from_k=rank)
+        visible = min(T, a.chunk) if a.chunk else T
+        mk = lambda v: torch.tensor(v, dtype=torch.int32, device=dev)   # noqa: E731
+        i = [0]
+        if decode:
+            q = torch.randn(B, qh * hd, device=dev).bfloat16()
+            out = torch.empty(B, qh * out_vd, device=dev, dtype=torch.bfloat16)
+            slots, pos = torch.arange(B, dtype=torch.int32, device=dev), torch.full((B,), T - 1, dtype=torch.int32, device=dev)
+
+            class Ctx:
+                sm_count = torch.cuda.get_device_properties(0).multi_processor_count
+            splits = a.splits or flex_decode_splits(Ctx, B, kvh, qh, visible)
+            scratch = torch.empty(max(1, ops.attention_flex_scratch_bytes(B, qh, kvh, out_vd, splits) // 4), device=dev)
+
+            def fn():
+                v = views[i[0] % copies]
+                i[0] += 1
+                ops.attention_flex_decode(q, out, v, slots, pos, B, qh, 1 / math.sqrt(hd), 0, extra, splits, scratch)
+            print(f"splits {splits}", file=sys.stderr)
+            timed(fn, B * visible * kvh * (hd + vd) * 2, 2.0 * B * qh * (hd + out_vd) * visible)
+        else:
+            q = torch.randn(T, qh * hd, device=dev).bfloat16()
+            out = torch.empty(T, qh * out_vd, device=dev, dtype=torch.bfloat16)
+            tr = ops.PREFILL_TILE_ROWS
+            n_tiles = (T + tr - 1) // tr
+            tile_seq, tile_row0 = mk([0] * n_tiles), mk(list(range(0, T, tr)))
+            first, sslot, spos0 = mk([0, T]), mk([0]), mk([0])
+            pairs = sum(min(p % a.chunk, p) + 1 if a.chunk else p + 1 for p in range(T))      # (query, key) pairs a row may see
+            timed(lambda: ops.attention_flex_prefill(q, out, views[0], tile_seq, tile_row0, n_tiles, first, sslot, spos0, qh,
+                                                     1 / math.sqrt(hd), 0, extra),
+                  T * qh * (hd + out_vd) * 2 + T * kvh * (hd + vd) * 2, 2.0 * qh * (hd + out_vd) * pairs)
+        return 0
+    if a.kernel == "glu_clipped":
+        rows, inter = a.m, a.n
+        gu = torch.randn(rows, 2 * inter, device=dev).bfloat16()
+        out = torch.empty(rows, inter, device=dev, dtype=torch.bfloat16)
+        copies = 1
+        timed(lambda: ops.glu_clipped(gu, out, rows, 7.0, 1.702, 1.0), rows * inter * 6)
+        return 0
     if a.kernel == "add_rmsnorm":
         rows, h = a.m, a.n
         resid, delta, w = torch.randn(rows, h, device=dev), bf(rows, h), torch.ones(h, device=dev).bfloat16()
@@ -655,6 +772,10 @@ def main(argv=None) -> int:
     k.add_argument("--kv-heads", type=int, default=8)
     k.add_argument("--head-dim", type=int, default=128)
     k.add_argument("--splits", type=int, default=0)
+    k.add_argument("--v-dim", type=int, default=0, help="attention_flex_*: width of a value row (default: head_dim)")
+    k.add_argument("--chunk", type=int, default=0, help="attention_flex_*: positions per chunk of the mask (0: none)")
+    k.add_argument("--latent-rank", type=int, default=0,
+                   help="attention_flex_*: the values are the first so many values of the key rows (kv-heads 1)")
     k.add_argument("--groups", type=int, default=1,
                    help="attention_decode: with --splits, how many thread-block clusters the splits of a (sequence, kv head) form")
     k.add_argument("--layers", type=int, default=36, help="decode_step (--impl reference): layers of the model")

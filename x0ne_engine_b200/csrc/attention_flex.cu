@@ -31,6 +31,21 @@ __device__ __forceinline__ void fx_ldmatrix_x4_trans(uint32_t& r0, uint32_t& r1,
     const uint32_t a = (uint32_t)__cvta_generic_to_shared(p);
     asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];" : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(a));
 }
+__device__ __forceinline__ void fx_ldmatrix_x4(uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3, const void* p) {
+    const uint32_t a = (uint32_t)__cvta_generic_to_shared(p);
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];" : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(a));
+}
+// 16 bytes from global to shared memory without passing through registers; zeros when `valid` is false
+// (nothing is read then: `src` only has to be an address of global memory)
+__device__ __forceinline__ void fx_cp16(bf16* dst, const bf16* src, bool valid) {
+    const uint32_t d = (uint32_t)__cvta_generic_to_shared(dst);
+    const int n = valid ? 16 : 0;
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(d), "l"(src), "r"(n) : "memory");
+}
+__device__ __forceinline__ void fx_cp_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void fx_cp_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
 __device__ __forceinline__ uint32_t fx_pack(float lo, float hi) {
     const __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
     return *reinterpret_cast<const uint32_t*>(&v);
@@ -66,6 +81,23 @@ __device__ __forceinline__ void fx_load_rows(bf16* dst, int stride, const bf16* 
     }
 }
 
+// The same through cp.async where rows can be copied 16 bytes at a time (the caller commits and waits);
+// other shapes, and a missing source, are written with plain stores.  `safe` is any address of global memory.
+__device__ __forceinline__ void fx_load_rows_async(bf16* dst, int stride, const bf16* src, int64_t src_ld, int n_rows, int r_lo, int r_hi,
+                                                   int d, int dp, int tid, int nthreads, const bf16* safe) {
+    const bool vec = src != nullptr && (d % 8 == 0) && (src_ld % 8 == 0) && ((((uintptr_t)src) & 15) == 0);
+    if (!vec) {
+        fx_load_rows(dst, stride, src, src_ld, n_rows, r_lo, r_hi, d, dp, tid, nthreads);
+        return;
+    }
+    const int per_row = dp / 8;
+    for (int i = tid; i < n_rows * per_row; i += nthreads) {
+        const int r = i / per_row, c = (i % per_row) * 8;
+        const bool ok = r >= r_lo && r <= r_hi && c < d;
+        fx_cp16(dst + r * stride + c, ok ? src + r * src_ld + c : safe, ok);
+    }
+}
+
 // The physical page of a sequence's logical page, or -1.
 __device__ __forceinline__ int fx_page(const PagedCache& c, int slot, int logical) {
     if (slot < 0) return -1;
@@ -87,18 +119,22 @@ struct FxShape {
 // S (16 rows of this warp x 8 n-tiles of 8 keys, starting at key tile row `key0`) = Q K^T.
 template <int NT>
 __device__ __forceinline__ void fx_scores(float (*s)[4], const bf16* qs, const bf16* ks, int stride, int dkp, int key0, int lane) {
-    const int g = lane >> 2, t = lane & 3;
+    const int mi = lane >> 3, r = lane & 7;
 #pragma unroll
     for (int n = 0; n < NT; ++n) s[n][0] = s[n][1] = s[n][2] = s[n][3] = 0.f;
+    // ldmatrix addresses of this lane: the query fragment (rows 0-7 / 8-15, k 0-7 / 8-15) and the key
+    // fragments of two n-tiles at once (keys 8n.. / 8(n+1).., k 0-7 / 8-15)
+    const bf16* qa = qs + ((mi & 1) * 8 + r) * stride + (mi >> 1) * 8;
+    const bf16* ka = ks + (key0 + (mi >> 1) * 8 + r) * stride + (mi & 1) * 8;
     for (int kk = 0; kk < dkp; kk += 16) {
-        const uint32_t a0 = *reinterpret_cast<const uint32_t*>(qs + g * stride + kk + 2 * t);
-        const uint32_t a1 = *reinterpret_cast<const uint32_t*>(qs + (g + 8) * stride + kk + 2 * t);
-        const uint32_t a2 = *reinterpret_cast<const uint32_t*>(qs + g * stride + kk + 8 + 2 * t);
-        const uint32_t a3 = *reinterpret_cast<const uint32_t*>(qs + (g + 8) * stride + kk + 8 + 2 * t);
+        uint32_t a0, a1, a2, a3;
+        fx_ldmatrix_x4(a0, a1, a2, a3, qa + kk);
 #pragma unroll
-        for (int n = 0; n < NT; ++n) {
-            const bf16* kr = ks + (key0 + 8 * n + g) * stride + kk + 2 * t;
-            fx_mma(s[n], a0, a1, a2, a3, *reinterpret_cast<const uint32_t*>(kr), *reinterpret_cast<const uint32_t*>(kr + 8));
+        for (int n = 0; n < NT; n += 2) {
+            uint32_t b0, b1, b2, b3;
+            fx_ldmatrix_x4(b0, b1, b2, b3, ka + 8 * n * stride + kk);
+            fx_mma(s[n], a0, a1, a2, a3, b0, b1);
+            fx_mma(s[n + 1], a0, a1, a2, a3, b2, b3);
         }
     }
 }
@@ -132,15 +168,16 @@ __device__ __forceinline__ void fx_accumulate(float (*o)[4], const float (*p)[4]
 // prefill
 // ------------------------------------------------------------------------------------------------
 template <int DVT>
-__global__ void __launch_bounds__(256, DVT > 12 ? 1 : 2)
+__global__ void __launch_bounds__(256, DVT > 16 ? 1 : 2)
 flex_prefill_kernel(const bf16* __restrict__ q, bf16* __restrict__ out, PagedCache cache, const int32_t* __restrict__ tile_seq,
                     const int32_t* __restrict__ tile_row0, const int32_t* __restrict__ seq_first_row,
                     const int32_t* __restrict__ seq_slot, const int32_t* __restrict__ seq_pos0, int q_heads, float scale,
                     int window, AttnExtra ex, FxShape sh) {
     extern __shared__ __align__(16) unsigned char fx_smem[];
+    // queries, then two stages of (key tile, value tile): the next page is copied while this one is used
     bf16* qs = reinterpret_cast<bf16*>(fx_smem);
-    bf16* ks = qs + FX_TILE_ROWS * sh.ks;
-    bf16* vs = ex.v_from_k > 0 ? ks : ks + FX_PAGE * sh.ks;
+    bf16* ks0 = qs + FX_TILE_ROWS * sh.ks;
+    const int stage_elems = FX_PAGE * sh.ks + (ex.v_from_k > 0 ? 0 : FX_PAGE * sh.vs);
     const int vstride = ex.v_from_k > 0 ? sh.ks : sh.vs;
     pdl_launch_dependents();
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, g = lane >> 2, t = lane & 3;
@@ -153,7 +190,8 @@ flex_prefill_kernel(const bf16* __restrict__ q, bf16* __restrict__ out, PagedCac
     const float sink2 = ex.sink != nullptr ? ex.sink[head] * FX_LOG2E : -INFINITY;
     pdl_wait();
     const int64_t q_ld = ex.q_ld > 0 ? ex.q_ld : (int64_t)q_heads * sh.dk;
-    fx_load_rows(qs, sh.ks, q + (int64_t)row0 * q_ld + (int64_t)head * sh.dk, q_ld, FX_TILE_ROWS, 0, n_rows - 1, sh.dk, sh.dkp, tid, 256);
+    const bf16* safe = (const bf16*)cache.base;
+    fx_load_rows_async(qs, sh.ks, q + (int64_t)row0 * q_ld + (int64_t)head * sh.dk, q_ld, FX_TILE_ROWS, 0, n_rows - 1, sh.dk, sh.dkp, tid, 256, safe);
 
     const float sc2 = scale * FX_LOG2E;
     const int r_a = warp * 16 + g, r_b = r_a + 8;                  // this thread's two rows of the tile
@@ -170,15 +208,36 @@ flex_prefill_kernel(const bf16* __restrict__ q, bf16* __restrict__ out, PagedCac
     const int key_lo = fx_first_key(pos0, window, ex.chunk), key_hi = pos0 + n_rows - 1;
     const int64_t k_head = (int64_t)kh * cache.page_size * sh.dk;
     const int64_t v_head = (int64_t)cache.kv_heads * cache.page_size * sh.dk + (int64_t)kh * cache.page_size * sh.vd;
-    for (int pg = key_lo / FX_PAGE; pg <= key_hi / FX_PAGE; ++pg) {
-        const int j0 = pg * FX_PAGE;
+    const int pg_first = key_lo / FX_PAGE, pg_last = key_hi / FX_PAGE;
+    auto issue = [&](int pg, int stage) -> bool {       // copies page pg into a stage; false if the sequence has no such page
         const int page = fx_page(cache, slot, pg);
         const bf16* pb = page >= 0 ? (const bf16*)cache.base + (int64_t)page * cache.page_stride : nullptr;
-        __syncthreads();          // the tile of the page before has been read (and q has arrived)
-        fx_load_rows(ks, sh.ks, pb ? pb + k_head : nullptr, sh.dk, FX_PAGE, 0, key_hi - j0, sh.dk, sh.dkp, tid, 256);
-        if (ex.v_from_k <= 0) fx_load_rows(vs, sh.vs, pb ? pb + v_head : nullptr, sh.vd, FX_PAGE, 0, key_hi - j0, sh.vd, sh.vdp, tid, 256);
-        __syncthreads();
-        if (warp * 16 >= n_rows || j0 > warp_last || j0 + FX_PAGE <= warp_first_key || pb == nullptr) continue;   // nothing of this page for this warp
+        bf16* kd = ks0 + stage * stage_elems;
+        fx_load_rows_async(kd, sh.ks, pb ? pb + k_head : nullptr, sh.dk, FX_PAGE, 0, key_hi - pg * FX_PAGE, sh.dk, sh.dkp, tid, 256, safe);
+        if (ex.v_from_k <= 0)
+            fx_load_rows_async(kd + FX_PAGE * sh.ks, sh.vs, pb ? pb + v_head : nullptr, sh.vd, FX_PAGE, 0, key_hi - pg * FX_PAGE, sh.vd, sh.vdp, tid, 256, safe);
+        fx_cp_commit();
+        return pb != nullptr;
+    };
+    bool have = issue(pg_first, 0);
+    for (int pg = pg_first; pg <= pg_last; ++pg) {
+        const int j0 = pg * FX_PAGE;
+        const int stage = (pg - pg_first) & 1;
+        const bf16* ks = ks0 + stage * stage_elems;
+        const bf16* vs = ex.v_from_k > 0 ? ks : ks + FX_PAGE * sh.ks;
+        const bool here = have;
+        if (pg < pg_last) {
+            have = issue(pg + 1, stage ^ 1);       // (the stage was last read two pages ago; the barrier at the end of that page covers it)
+            fx_cp_wait<1>();
+        } else {
+            fx_cp_wait<0>();
+        }
+        __syncthreads();          // this page's tile (and, the first time, the queries) is complete for every warp
+        const bool skip = !here;
+        if (warp * 16 >= n_rows || j0 > warp_last || j0 + FX_PAGE <= warp_first_key || skip) {   // nothing of this page for this warp
+            __syncthreads();
+            continue;
+        }
         float s[8][4];
         fx_scores<8>(s, qs + warp * 16 * sh.ks, ks, sh.ks, sh.dkp, 0, lane);
         float mx_a = -INFINITY, mx_b = -INFINITY;
@@ -215,6 +274,7 @@ flex_prefill_kernel(const bf16* __restrict__ q, bf16* __restrict__ out, PagedCac
 #pragma unroll
         for (int n = 0; n < DVT; ++n) { o[n][0] *= al_a; o[n][1] *= al_a; o[n][2] *= al_b; o[n][3] *= al_b; }
         fx_accumulate<DVT, 4>(o, s, vs, vstride, 0, lane);
+        __syncthreads();          // every warp is done with this stage before the page after next is copied into it
     }
     // the row's sum over its four threads, the sink, the gate, and out
     l_a += __shfl_xor_sync(0xffffffffu, l_a, 1); l_a += __shfl_xor_sync(0xffffffffu, l_a, 2);
@@ -260,10 +320,10 @@ flex_decode_kernel(const bf16* __restrict__ q, bf16* __restrict__ out, PagedCach
                    int chunks, int splits, float* __restrict__ scratch) {
     extern __shared__ __align__(16) unsigned char fx_smem[];
     bf16* qs = reinterpret_cast<bf16*>(fx_smem);
-    bf16* ks = qs + 16 * sh.ks;
-    bf16* vs = ex.v_from_k > 0 ? ks : ks + FX_PAGE * sh.ks;
+    bf16* ks0 = qs + 16 * sh.ks;
+    const int stage_elems = FX_PAGE * sh.ks + (ex.v_from_k > 0 ? 0 : FX_PAGE * sh.vs);
     const int vstride = ex.v_from_k > 0 ? sh.ks : sh.vs;
-    float* mg = reinterpret_cast<float*>(ks);          // the warps' partial results meet here at the end
+    float* mg = reinterpret_cast<float*>(ks0);         // the warps' partial results meet here at the end
     pdl_launch_dependents();
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, g = lane >> 2, t = lane & 3;
     const int group = q_heads / cache.kv_heads;
@@ -273,7 +333,8 @@ flex_decode_kernel(const bf16* __restrict__ q, bf16* __restrict__ out, PagedCach
     const int head0 = kh * group + chunk_i * 16, n_items = min(16, group - chunk_i * 16);
     pdl_wait();
     const int64_t q_ld = ex.q_ld > 0 ? ex.q_ld : (int64_t)q_heads * sh.dk;
-    fx_load_rows(qs, sh.ks, q + (int64_t)row * q_ld + (int64_t)head0 * sh.dk, sh.dk, 16, 0, n_items - 1, sh.dk, sh.dkp, tid, 128);
+    const bf16* safe = (const bf16*)cache.base;
+    fx_load_rows_async(qs, sh.ks, q + (int64_t)row * q_ld + (int64_t)head0 * sh.dk, sh.dk, 16, 0, n_items - 1, sh.dk, sh.dkp, tid, 128, safe);
 
     const float sc2 = scale * FX_LOG2E;
     const int key_lo = fx_first_key(pos, window, ex.chunk);
@@ -286,16 +347,39 @@ flex_decode_kernel(const bf16* __restrict__ q, bf16* __restrict__ out, PagedCach
     for (int n = 0; n < DVT; ++n) o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.f;
     const int64_t k_head = (int64_t)kh * cache.page_size * sh.dk;
     const int64_t v_head = (int64_t)cache.kv_heads * cache.page_size * sh.dk + (int64_t)kh * cache.page_size * sh.vd;
-    for (int pg = pg_a; pg <= pg_b; ++pg) {
-        const int j0 = pg * FX_PAGE;
+    auto issue = [&](int pg, int stage) -> bool {
         const int page = fx_page(cache, slot, pg);
         const bf16* pb = page >= 0 ? (const bf16*)cache.base + (int64_t)page * cache.page_stride : nullptr;
-        __syncthreads();
-        fx_load_rows(ks, sh.ks, pb ? pb + k_head : nullptr, sh.dk, FX_PAGE, 0, pos - j0, sh.dk, sh.dkp, tid, 128);
-        if (ex.v_from_k <= 0) fx_load_rows(vs, sh.vs, pb ? pb + v_head : nullptr, sh.vd, FX_PAGE, 0, pos - j0, sh.vd, sh.vdp, tid, 128);
+        bf16* kd = ks0 + stage * stage_elems;
+        fx_load_rows_async(kd, sh.ks, pb ? pb + k_head : nullptr, sh.dk, FX_PAGE, 0, pos - pg * FX_PAGE, sh.dk, sh.dkp, tid, 128, safe);
+        if (ex.v_from_k <= 0)
+            fx_load_rows_async(kd + FX_PAGE * sh.ks, sh.vs, pb ? pb + v_head : nullptr, sh.vd, FX_PAGE, 0, pos - pg * FX_PAGE, sh.vd, sh.vdp, tid, 128, safe);
+        fx_cp_commit();
+        return pb != nullptr;
+    };
+    bool have = pg_a <= pg_b ? issue(pg_a, 0) : false;
+    if (pg_a > pg_b) {                       // (no page for this split: only the queries are in flight)
+        fx_cp_commit();
+        fx_cp_wait<0>();
+    }
+    for (int pg = pg_a; pg <= pg_b; ++pg) {
+        const int j0 = pg * FX_PAGE;
+        const int stage = (pg - pg_a) & 1;
+        const bf16* ks = ks0 + stage * stage_elems;
+        const bf16* vs = ex.v_from_k > 0 ? ks : ks + FX_PAGE * sh.ks;
+        const bool here = have;
+        if (pg < pg_b) {
+            have = issue(pg + 1, stage ^ 1);
+            fx_cp_wait<1>();
+        } else {
+            fx_cp_wait<0>();
+        }
         __syncthreads();
         const int jw = j0 + 16 * warp;           // this warp's 16 keys of the page
-        if (pb == nullptr || jw > pos || jw + 16 <= key_lo) continue;
+        if (!here || jw > pos || jw + 16 <= key_lo) {
+            __syncthreads();
+            continue;
+        }
         float s[2][4];
         fx_scores<2>(s, qs, ks, sh.ks, sh.dkp, 16 * warp, lane);
 #pragma unroll
@@ -332,6 +416,7 @@ flex_decode_kernel(const bf16* __restrict__ q, bf16* __restrict__ out, PagedCach
 #pragma unroll
         for (int n = 0; n < DVT; ++n) { o[n][0] *= al_a; o[n][1] *= al_a; o[n][2] *= al_b; o[n][3] *= al_b; }
         fx_accumulate<DVT, 1>(o, s, vs, vstride, 16 * warp, lane);
+        __syncthreads();
     }
     l_a += __shfl_xor_sync(0xffffffffu, l_a, 1); l_a += __shfl_xor_sync(0xffffffffu, l_a, 2);
     l_b += __shfl_xor_sync(0xffffffffu, l_b, 1); l_b += __shfl_xor_sync(0xffffffffu, l_b, 2);
@@ -388,37 +473,52 @@ flex_decode_kernel(const bf16* __restrict__ q, bf16* __restrict__ out, PagedCach
     }
 }
 
-// Merges the splits of every unit in split order and writes the rows out.  One block of 128 threads per unit.
-__global__ void flex_decode_merge_kernel(const float* __restrict__ scratch, bf16* __restrict__ out, int q_heads, int kv_heads,
-                                         AttnExtra ex, int vd, int vdp, int chunks, int splits) {
+// Merges the splits of every unit in split order and writes the rows out.  One block of 256 threads per
+// unit: 16 threads per item (q head), each with every 16th column; the splits' weights 2^(m_s - m) are
+// worked out once per item and kept in shared memory.
+#define FX_MAX_SPLITS 64
+__global__ void __launch_bounds__(256)
+flex_decode_merge_kernel(const float* __restrict__ scratch, bf16* __restrict__ out, int q_heads, int kv_heads,
+                         AttnExtra ex, int vd, int vdp, int chunks, int splits) {
+    __shared__ float wgt[16][FX_MAX_SPLITS];
+    __shared__ float fin_s[16];
     pdl_prologue();
     const int unit = blockIdx.x, tid = threadIdx.x;
     const int group = q_heads / kv_heads;
     const int chunk_i = unit % chunks, kh = (unit / chunks) % kv_heads, row = unit / (chunks * kv_heads);
     const int head0 = kh * group + chunk_i * 16, n_items = min(16, group - chunk_i * 16);
-    const int item = tid >> 3, c0 = tid & 7, ps = vdp + 2;
-    if (item >= n_items) return;
+    const int item = tid >> 4, c0 = tid & 15, ps = vdp + 2;
     const float* src = scratch + ((int64_t)unit * splits * 16 + item) * ps;
     const int64_t step = (int64_t)16 * ps;
-    float mm = -INFINITY;
-    for (int s = 0; s < splits; ++s) mm = fmaxf(mm, src[s * step]);
-    const float ref = mm == -INFINITY ? 0.f : mm;
-    float ll = 0.f;
-    for (int s = 0; s < splits; ++s) ll += src[s * step + 1] * exp2f(src[s * step] - ref);
-    const int head = head0 + item;
-    float fin = 1.f;
-    if (ex.sink != nullptr) {
-        const float sink2 = ex.sink[head] * FX_LOG2E;
-        const float mf = fmaxf(mm, sink2);
-        fin = exp2f(mm - mf);
-        ll = ll * fin + exp2f(sink2 - mf);
+    if (c0 == 0 && item < n_items) {
+        float mm = -INFINITY;
+        for (int s = 0; s < splits; ++s) mm = fmaxf(mm, src[s * step]);
+        const float ref = mm == -INFINITY ? 0.f : mm;
+        float ll = 0.f;
+        for (int s = 0; s < splits; ++s) {
+            const float f = exp2f(src[s * step] - ref);
+            wgt[item][s] = f;
+            ll += src[s * step + 1] * f;
+        }
+        const int head = head0 + item;
+        float fin = 1.f;
+        if (ex.sink != nullptr) {
+            const float sink2 = ex.sink[head] * FX_LOG2E;
+            const float mf = fmaxf(mm, sink2);
+            fin = exp2f(mm - mf);
+            ll = ll * fin + exp2f(sink2 - mf);
+        }
+        fin *= ll > 0.f ? 1.0f / ll : 0.f;
+        if (ex.gate != nullptr) fin *= 1.0f / (1.0f + expf(-__bfloat162float(((const bf16*)ex.gate)[(int64_t)row * ex.gate_ld + head])));
+        fin_s[item] = fin;
     }
-    fin *= ll > 0.f ? 1.0f / ll : 0.f;
-    if (ex.gate != nullptr) fin *= 1.0f / (1.0f + expf(-__bfloat162float(((const bf16*)ex.gate)[(int64_t)row * ex.gate_ld + head])));
-    bf16* orow = out + ((int64_t)row * q_heads + head) * vd;
-    for (int c = c0; c < vd; c += 8) {
+    __syncthreads();
+    if (item >= n_items) return;
+    const float fin = fin_s[item];
+    bf16* orow = out + ((int64_t)row * q_heads + head0 + item) * vd;
+    for (int c = c0; c < vd; c += 16) {
         float acc = 0.f;
-        for (int s = 0; s < splits; ++s) acc += src[s * step + 2 + c] * exp2f(src[s * step] - ref);
+        for (int s = 0; s < splits; ++s) acc += src[s * step + 2 + c] * wgt[item][s];
         orow[c] = __float2bfloat16_rn(acc * fin);
     }
 }
@@ -455,10 +555,10 @@ static int fx_shape(const PagedCache& cache, const AttnExtra& ex, FxShape* sh) {
 }
 
 static size_t fx_prefill_smem(const FxShape& sh, bool v_from_k) {
-    return ((size_t)(FX_TILE_ROWS + FX_PAGE) * sh.ks + (v_from_k ? 0 : (size_t)FX_PAGE * sh.vs)) * sizeof(bf16);
+    return ((size_t)(FX_TILE_ROWS + 2 * FX_PAGE) * sh.ks + (v_from_k ? 0 : (size_t)2 * FX_PAGE * sh.vs)) * sizeof(bf16);
 }
 static size_t fx_decode_smem(const FxShape& sh, bool v_from_k) {
-    const size_t tiles = ((size_t)FX_PAGE * sh.ks + (v_from_k ? 0 : (size_t)FX_PAGE * sh.vs)) * sizeof(bf16);
+    const size_t tiles = 2 * ((size_t)FX_PAGE * sh.ks + (v_from_k ? 0 : (size_t)FX_PAGE * sh.vs)) * sizeof(bf16);
     const size_t merge = (size_t)4 * 16 * (sh.vdp + 2) * sizeof(float);
     return (size_t)16 * sh.ks * sizeof(bf16) + (tiles > merge ? tiles : merge);
 }
@@ -526,7 +626,7 @@ X0NE_API int x0ne_attention_flex_decode(const void* q, void* out, PagedCache cac
                                         int splits, void* scratch, int64_t scratch_bytes, cudaStream_t stream) {
     X0NE_REQUIRE(n_rows >= 0 && q_heads > 0 && cache.kv_heads > 0 && q_heads % cache.kv_heads == 0,
                  "attention_flex: %d q heads over %d kv heads", q_heads, cache.kv_heads);
-    X0NE_REQUIRE(window >= 0 && ex.chunk >= 0 && splits >= 1 && splits <= 65535, "attention_flex: window, chunk or splits out of range");
+    X0NE_REQUIRE(window >= 0 && ex.chunk >= 0 && splits >= 1 && splits <= FX_MAX_SPLITS, "attention_flex: window, chunk or splits (1 to %d) out of range", FX_MAX_SPLITS);
     FxShape sh;
     if (int e = fx_shape(cache, ex, &sh)) return e;
     if (n_rows == 0) return 0;
@@ -559,7 +659,7 @@ X0NE_API int x0ne_attention_flex_decode(const void* q, void* out, PagedCache cac
     if (splits > 1) {
         cudaError_t e = cudaGetLastError();
         X0NE_REQUIRE(e == cudaSuccess, "attention_flex: %s", cudaGetErrorString(e));
-        x0ne_launch(flex_decode_merge_kernel, dim3((unsigned)units), dim3(128), 0, stream, (const float*)scratch, (bf16*)out, q_heads,
+        x0ne_launch(flex_decode_merge_kernel, dim3((unsigned)units), dim3(256), 0, stream, (const float*)scratch, (bf16*)out, q_heads,
                     cache.kv_heads, ex, sh.vd, sh.vdp, chunks, splits);
     }
     X0NE_LAUNCH_CHECK();

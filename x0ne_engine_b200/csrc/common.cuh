@@ -182,6 +182,20 @@ struct PagedCache {
 
 __host__ __device__ __forceinline__ int cache_v_dim(const PagedCache& c) { return c.v_dim == 0 ? c.head_dim : (c.v_dim > 0 ? c.v_dim : 0); }
 
+// The gated activation a product's epilogue applies to a (gate, up) pair.  limit <= 0: silu(g) u.  Else the
+// clipped unit: g = min(g, limit), u = clamp(u, -limit, limit), g sigmoid(slope g) (u + shift).
+struct GluParams {
+    float limit, slope, shift;
+};
+__device__ __forceinline__ float glu_act(float g, float u, const GluParams& p) {
+    if (p.limit > 0.f) {
+        g = fminf(g, p.limit);
+        u = fminf(fmaxf(u, -p.limit), p.limit);
+        return g / (1.0f + expf(-p.slope * g)) * (u + p.shift);
+    }
+    return g / (1.0f + expf(-g)) * u;
+}
+
 // What an attention kernel may be asked for beyond causal softmax over a window.  All zero: nothing.
 struct AttnExtra {
     int32_t chunk;        // > 0: a query sees the keys of its own chunk of this many positions only

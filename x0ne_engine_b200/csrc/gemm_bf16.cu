@@ -53,7 +53,7 @@ template <int N> __device__ __forceinline__ void cp_wait() { asm volatile("cp.as
 template <int MT, typename OutT, bool SWIGLU, int DEPTH>
 __global__ void __launch_bounds__(SM_WARPS * 32) gemm_smallm_kernel(const bf16* __restrict__ W, const bf16* __restrict__ X,
                                                                     OutT* __restrict__ Y, int M, int N, int K, int ldy,
-                                                                    int n_tiles) {
+                                                                    int n_tiles, GluParams glu) {
     constexpr int SETS = SWIGLU ? 2 : 1;
     extern __shared__ __align__(16) unsigned char smem_raw[];
     constexpr int SLOTS = SETS * 2 + MT;     // 16-byte pieces per chunk and thread: weight rows, then activation rows
@@ -178,7 +178,7 @@ __global__ void __launch_bounds__(SM_WARPS * 32) gemm_smallm_kernel(const bf16* 
             }
             if (n < N && m < M) {
                 float out = v[0];
-                if (SWIGLU) out = v[0] / (1.0f + expf(-v[0])) * v[SETS - 1];
+                if (SWIGLU) out = glu_act(v[0], v[SETS - 1], glu);
                 Y[(int64_t)m * ldy + n] = from_f32<OutT>(out);
             }
         }
@@ -188,7 +188,7 @@ __global__ void __launch_bounds__(SM_WARPS * 32) gemm_smallm_kernel(const bf16* 
 }
 
 template <int MT, typename OutT, bool SWIGLU>
-static int launch_smallm(const bf16* W, const bf16* X, OutT* Y, int M, int N, int K, int ldy, int sms, cudaStream_t stream) {
+static int launch_smallm(const bf16* W, const bf16* X, OutT* Y, int M, int N, int K, int ldy, int sms, GluParams glu, cudaStream_t stream) {
     constexpr int SETS = SWIGLU ? 2 : 1;
     constexpr int SLOTS = SETS * 2 + MT;
     constexpr int DEPTH = smallm_depth(MT, SWIGLU);
@@ -215,14 +215,16 @@ static int launch_smallm(const bf16* W, const bf16* X, OutT* Y, int M, int N, in
     const int resident = sms * per_sm;
     const int tiles_per_block = (n_tiles + resident - 1) / resident;
     const int grid = (n_tiles + tiles_per_block - 1) / tiles_per_block;
-    x0ne_launch(gemm_smallm_kernel<MT, OutT, SWIGLU, DEPTH>, dim3(grid), dim3(SM_WARPS * 32), SMEM, stream, W, X, Y, M, N, K, ldy, n_tiles);
+    x0ne_launch(gemm_smallm_kernel<MT, OutT, SWIGLU, DEPTH>, dim3(grid), dim3(SM_WARPS * 32), SMEM, stream, W, X, Y, M, N, K, ldy, n_tiles, glu);
     X0NE_LAUNCH_CHECK();
 }
 
 // out_kind: 0 = bfloat16, 1 = float32, 2 = bfloat16 with SwiGLU over the packed [gate; up] weight
 // (W then has 2*N rows and y has N columns).
-X0NE_API int x0ne_gemm_bf16_smallm(const void* W, const void* X, void* Y, int M, int N, int K, int ldy, int out_kind,
-                                   int sms, cudaStream_t stream) {
+// With out_kind 2, (limit, slope, shift) choose the gated activation (`GluParams`; limit 0: SwiGLU).
+X0NE_API int x0ne_gemm_bf16_smallm_glu(const void* W, const void* X, void* Y, int M, int N, int K, int ldy, int out_kind,
+                                       int sms, float limit, float slope, float shift, cudaStream_t stream) {
+    const GluParams glu = {limit, slope, shift};
     X0NE_REQUIRE(M >= 0 && M <= 32 && N > 0 && K > 0, "gemm_smallm: M %d (at most 32) N %d K %d", M, N, K);
     X0NE_REQUIRE(K % 8 == 0, "gemm_smallm: K %d is not a multiple of 8", K);
     X0NE_REQUIRE(ldy >= N && sms > 0 && out_kind >= 0 && out_kind <= 2, "gemm_smallm: ldy %d N %d kind %d", ldy, N, out_kind);
@@ -232,11 +234,16 @@ X0NE_API int x0ne_gemm_bf16_smallm(const void* W, const void* X, void* Y, int M,
     const bf16* x = (const bf16*)X;
     const int mt = (M + 7) / 8;
 #define X0NE_SMALLM(MT)                                                                                        \
-    if (out_kind == 0) return launch_smallm<MT, bf16, false>(w, x, (bf16*)Y, M, N, K, ldy, sms, stream);       \
-    if (out_kind == 1) return launch_smallm<MT, float, false>(w, x, (float*)Y, M, N, K, ldy, sms, stream);     \
-    return launch_smallm<MT, bf16, true>(w, x, (bf16*)Y, M, N, K, ldy, sms, stream);
+    if (out_kind == 0) return launch_smallm<MT, bf16, false>(w, x, (bf16*)Y, M, N, K, ldy, sms, glu, stream);       \
+    if (out_kind == 1) return launch_smallm<MT, float, false>(w, x, (float*)Y, M, N, K, ldy, sms, glu, stream);     \
+    return launch_smallm<MT, bf16, true>(w, x, (bf16*)Y, M, N, K, ldy, sms, glu, stream);
     if (mt == 1) { X0NE_SMALLM(1) }
     if (mt == 2) { X0NE_SMALLM(2) }
     { X0NE_SMALLM(4) }
 #undef X0NE_SMALLM
+}
+
+X0NE_API int x0ne_gemm_bf16_smallm(const void* W, const void* X, void* Y, int M, int N, int K, int ldy, int out_kind,
+                                   int sms, cudaStream_t stream) {
+    return x0ne_gemm_bf16_smallm_glu(W, X, Y, M, N, K, ldy, out_kind, sms, 0.f, 0.f, 0.f, stream);
 }

@@ -64,7 +64,7 @@ template <bool SWIGLU, typename OutT>
 __global__ void __launch_bounds__(SK_THREADS, 2) gemm_skinny_tc_kernel(const __grid_constant__ CUtensorMap map_x,
                                                                        const __grid_constant__ CUtensorMap map_w,
                                                                        OutT* __restrict__ Y, int M, int N, int K, int ldy,
-                                                                       int mma_n, int* status) {
+                                                                       int mma_n, int* status, GluParams glu) {
     extern __shared__ unsigned char sk_raw[];
     unsigned char* base = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(sk_raw) + 1023) & ~(uintptr_t)1023);
     constexpr int A_BYTES = 128 * 128, B_BYTES = SK_XROWS * 128, STAGE_BYTES = A_BYTES + B_BYTES;
@@ -215,7 +215,7 @@ __global__ void __launch_bounds__(SK_THREADS, 2) gemm_skinny_tc_kernel(const __g
             if (SWIGLU) {
                 const float u4[4] = {us.x, us.y, us.z, us.w};
 #pragma unroll
-                for (int i = 0; i < 4; ++i) o4[i] = o4[i] / (1.0f + expf(-o4[i])) * u4[i];
+                for (int i = 0; i < 4; ++i) o4[i] = glu_act(o4[i], u4[i], glu);
             }
             const int n = n0 + c;
             OutT* dst = Y + (int64_t)m * ldy + n;
@@ -237,7 +237,7 @@ __global__ void __launch_bounds__(SK_THREADS, 2) gemm_skinny_tc_kernel(const __g
 int x0ne_tc_make_map(CUtensorMap* map, const void* ptr, int64_t rows, int64_t cols, int box_rows);
 
 template <bool SWIGLU, typename OutT>
-static int launch_skinny(const void* W, const void* X, int x_rows, OutT* Y, int M, int N, int K, int ldy, int* status,
+static int launch_skinny(const void* W, const void* X, int x_rows, OutT* Y, int M, int N, int K, int ldy, int* status, GluParams glu,
                          cudaStream_t stream) {
     CUtensorMap map_x, map_w;
     // The map covers the rows x really has (up to the tile's 64): rows past M then come from memory
@@ -279,24 +279,31 @@ static int launch_skinny(const void* W, const void* X, int x_rows, OutT* Y, int 
     const int mma_n = (M + 15) / 16 * 16;
     if (slices > 1)
         x0ne_launch_clusters(gemm_skinny_tc_kernel<SWIGLU, OutT>, dim3(slices, tiles), dim3(SK_THREADS), slices, smem, stream, map_x,
-                             map_w, Y, M, N, K, ldy, mma_n, status);
+                             map_w, Y, M, N, K, ldy, mma_n, status, glu);
     else
         x0ne_launch(gemm_skinny_tc_kernel<SWIGLU, OutT>, dim3(1, tiles), dim3(SK_THREADS), smem, stream, map_x, map_w, Y, M, N, K,
-                    ldy, mma_n, status);
+                    ldy, mma_n, status, glu);
     X0NE_LAUNCH_CHECK();
 }
 
 // out_kind: 0 = bfloat16, 1 = float32, 2 = bfloat16 with SwiGLU over the packed [gate; up] weight
 // (W then has 2*N rows and y has N columns).  `status` as for the other tcgen05 kernels.
 // `x_rows`: rows allocated behind X (at least M).
-X0NE_API int x0ne_gemm_bf16_skinny_tcgen05(const void* W, const void* X, int x_rows, void* Y, int M, int N, int K, int ldy,
-                                           int out_kind, int* status, cudaStream_t stream) {
+// With out_kind 2, (limit, slope, shift) choose the gated activation (`GluParams`; limit 0: SwiGLU).
+X0NE_API int x0ne_gemm_bf16_skinny_tcgen05_glu(const void* W, const void* X, int x_rows, void* Y, int M, int N, int K, int ldy,
+                                               int out_kind, int* status, float limit, float slope, float shift, cudaStream_t stream) {
+    const GluParams glu = {limit, slope, shift};
     X0NE_REQUIRE(M >= 0 && M <= 64 && N > 0 && K > 0 && x_rows >= M, "gemm_skinny_tc: M %d (at most 64, x has %d rows) N %d K %d", M, x_rows, N, K);
     X0NE_REQUIRE(K % 8 == 0, "gemm_skinny_tc: K %d is not a multiple of 8 (rows must be 16-byte aligned for TMA)", K);
     X0NE_REQUIRE(ldy >= N && out_kind >= 0 && out_kind <= 2 && status != nullptr, "gemm_skinny_tc: ldy %d N %d kind %d", ldy, N, out_kind);
     X0NE_REQUIRE((((uintptr_t)W | (uintptr_t)X) & 15) == 0, "gemm_skinny_tc: operands are not 16-byte aligned");
     if (M == 0) return 0;
-    if (out_kind == 0) return launch_skinny<false, bf16>(W, X, x_rows, (bf16*)Y, M, N, K, ldy, status, stream);
-    if (out_kind == 1) return launch_skinny<false, float>(W, X, x_rows, (float*)Y, M, N, K, ldy, status, stream);
-    return launch_skinny<true, bf16>(W, X, x_rows, (bf16*)Y, M, N, K, ldy, status, stream);
+    if (out_kind == 0) return launch_skinny<false, bf16>(W, X, x_rows, (bf16*)Y, M, N, K, ldy, status, glu, stream);
+    if (out_kind == 1) return launch_skinny<false, float>(W, X, x_rows, (float*)Y, M, N, K, ldy, status, glu, stream);
+    return launch_skinny<true, bf16>(W, X, x_rows, (bf16*)Y, M, N, K, ldy, status, glu, stream);
+}
+
+X0NE_API int x0ne_gemm_bf16_skinny_tcgen05(const void* W, const void* X, int x_rows, void* Y, int M, int N, int K, int ldy,
+                                           int out_kind, int* status, cudaStream_t stream) {
+    return x0ne_gemm_bf16_skinny_tcgen05_glu(W, X, x_rows, Y, M, N, K, ldy, out_kind, status, 0.f, 0.f, 0.f, stream);
 }

@@ -47,7 +47,7 @@ template <bool SWIGLU, typename OutT>
 __global__ void __launch_bounds__(TC_THREADS) gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x,
                                                              const __grid_constant__ CUtensorMap map_w, OutT* __restrict__ Y,
                                                              int M, int N, int K, int ldy, int m_tiles, int n_tiles,
-                                                             int* status) {
+                                                             int* status, GluParams glu) {
     extern __shared__ unsigned char tc_raw[];
     // tiles need 1024-byte alignment for the 128-byte swizzle
     unsigned char* base = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(tc_raw) + 1023) & ~(uintptr_t)1023);
@@ -167,7 +167,7 @@ __global__ void __launch_bounds__(TC_THREADS) gemm_tc_kernel(const __grid_consta
                     float u[32];
                     tc_ld32(trow + 128 + c * 32, u);
 #pragma unroll
-                    for (int i = 0; i < 32; ++i) v[i] = v[i] / (1.0f + expf(-v[i])) * u[i];
+                    for (int i = 0; i < 32; ++i) v[i] = glu_act(v[i], u[i], glu);
                 }
                 const int n = n0 + c * 32;
                 if (m < M) {
@@ -257,7 +257,7 @@ template <bool SWIGLU, typename OutT>
 __global__ void __launch_bounds__(TC_THREADS) gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_x,
                                                                   const __grid_constant__ CUtensorMap map_w,
                                                                   OutT* __restrict__ Y, int M, int N, int K, int ldy,
-                                                                  int m_tiles, int n_tiles, int* status) {
+                                                                  int m_tiles, int n_tiles, int* status, GluParams glu) {
     extern __shared__ unsigned char tc_raw[];
     unsigned char* base = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(tc_raw) + 1023) & ~(uintptr_t)1023);
     constexpr int A_BYTES = 128 * 128, B_BYTES = 128 * 128, STAGE_BYTES = A_BYTES + B_BYTES;
@@ -367,7 +367,7 @@ __global__ void __launch_bounds__(TC_THREADS) gemm_tc_pair_kernel(const __grid_c
                     float u[32];
                     tc_ld32(trow + 128 + c * 32, u);
 #pragma unroll
-                    for (int i = 0; i < 32; ++i) v[i] = v[i] / (1.0f + expf(-v[i])) * u[i];
+                    for (int i = 0; i < 32; ++i) v[i] = glu_act(v[i], u[i], glu);
                 }
                 const int n = n0 + c * 32;
                 if (m < M) {
@@ -429,7 +429,7 @@ int x0ne_tc_make_map(CUtensorMap* map, const void* ptr, int64_t rows, int64_t co
 }
 
 template <bool SWIGLU, typename OutT>
-static int launch_tc(const void* W, const void* X, OutT* Y, int M, int N, int K, int ldy, int* status, cudaStream_t stream) {
+static int launch_tc(const void* W, const void* X, OutT* Y, int M, int N, int K, int ldy, int* status, GluParams glu, cudaStream_t stream) {
     CUtensorMap map_x, map_w;
     if (int e = x0ne_tc_make_map(&map_x, X, M, K, TC_BM)) return e;
     if (int e = x0ne_tc_make_map(&map_w, W, SWIGLU ? 2 * (int64_t)N : N, K, SWIGLU ? 128 : 256)) return e;
@@ -453,12 +453,12 @@ static int launch_tc(const void* W, const void* X, OutT* Y, int M, int N, int K,
     const int tiles = n_tiles * m_tiles;
     const int grid = tiles < sms ? tiles : sms;      // one persistent block per SM (shared memory allows no more)
     x0ne_launch(gemm_tc_kernel<SWIGLU, OutT>, dim3(grid), dim3(TC_THREADS), smem, stream, map_x, map_w, Y, M, N, K, ldy, m_tiles,
-                n_tiles, status);
+                n_tiles, status, glu);
     X0NE_LAUNCH_CHECK();
 }
 
 template <bool SWIGLU, typename OutT>
-static int launch_tc_pair(const void* W, const void* X, OutT* Y, int M, int N, int K, int ldy, int* status, cudaStream_t stream) {
+static int launch_tc_pair(const void* W, const void* X, OutT* Y, int M, int N, int K, int ldy, int* status, GluParams glu, cudaStream_t stream) {
     CUtensorMap map_x, map_w;
     if (int e = x0ne_tc_make_map(&map_x, X, M, K, 128)) return e;
     if (int e = x0ne_tc_make_map(&map_w, W, SWIGLU ? 2 * (int64_t)N : N, K, 128)) return e;
@@ -493,7 +493,7 @@ static int launch_tc_pair(const void* W, const void* X, OutT* Y, int M, int N, i
     attr[0].val.clusterDim.z = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    cudaLaunchKernelEx(&cfg, gemm_tc_pair_kernel<SWIGLU, OutT>, map_x, map_w, Y, M, N, K, ldy, m_tiles, n_tiles, status);
+    cudaLaunchKernelEx(&cfg, gemm_tc_pair_kernel<SWIGLU, OutT>, map_x, map_w, Y, M, N, K, ldy, m_tiles, n_tiles, status, glu);
     X0NE_LAUNCH_CHECK();
 }
 
@@ -502,18 +502,25 @@ static int launch_tc_pair(const void* W, const void* X, OutT* Y, int M, int N, i
 // first call; a non-zero value afterwards says a barrier wait ran out (1 copy, 2 MMA, 3 epilogue)
 // and the output is not valid.
 // `pair` = 1 uses pairs of blocks (256 x 256 tiles), 0 single blocks (128 x 256 tiles).
-X0NE_API int x0ne_gemm_bf16_tcgen05(const void* W, const void* X, void* Y, int M, int N, int K, int ldy, int out_kind,
-                                    int pair, int* status, cudaStream_t stream) {
+// With out_kind 2, (limit, slope, shift) choose the gated activation (`GluParams`; limit 0: SwiGLU).
+X0NE_API int x0ne_gemm_bf16_tcgen05_glu(const void* W, const void* X, void* Y, int M, int N, int K, int ldy, int out_kind,
+                                        int pair, int* status, float limit, float slope, float shift, cudaStream_t stream) {
+    const GluParams glu = {limit, slope, shift};
     X0NE_REQUIRE(M > 0 && N > 0 && K > 0, "gemm_tc: M %d N %d K %d", M, N, K);
     X0NE_REQUIRE(K % 8 == 0, "gemm_tc: K %d is not a multiple of 8 (rows must be 16-byte aligned)", K);
     X0NE_REQUIRE(ldy >= N && out_kind >= 0 && out_kind <= 2 && status != nullptr, "gemm_tc: ldy %d N %d kind %d", ldy, N, out_kind);
     X0NE_REQUIRE((((uintptr_t)W | (uintptr_t)X) & 15) == 0, "gemm_tc: operands are not 16-byte aligned");
     if (pair) {
-        if (out_kind == 0) return launch_tc_pair<false, bf16>(W, X, (bf16*)Y, M, N, K, ldy, status, stream);
-        if (out_kind == 1) return launch_tc_pair<false, float>(W, X, (float*)Y, M, N, K, ldy, status, stream);
-        return launch_tc_pair<true, bf16>(W, X, (bf16*)Y, M, N, K, ldy, status, stream);
+        if (out_kind == 0) return launch_tc_pair<false, bf16>(W, X, (bf16*)Y, M, N, K, ldy, status, glu, stream);
+        if (out_kind == 1) return launch_tc_pair<false, float>(W, X, (float*)Y, M, N, K, ldy, status, glu, stream);
+        return launch_tc_pair<true, bf16>(W, X, (bf16*)Y, M, N, K, ldy, status, glu, stream);
     }
-    if (out_kind == 0) return launch_tc<false, bf16>(W, X, (bf16*)Y, M, N, K, ldy, status, stream);
-    if (out_kind == 1) return launch_tc<false, float>(W, X, (float*)Y, M, N, K, ldy, status, stream);
-    return launch_tc<true, bf16>(W, X, (bf16*)Y, M, N, K, ldy, status, stream);
+    if (out_kind == 0) return launch_tc<false, bf16>(W, X, (bf16*)Y, M, N, K, ldy, status, glu, stream);
+    if (out_kind == 1) return launch_tc<false, float>(W, X, (float*)Y, M, N, K, ldy, status, glu, stream);
+    return launch_tc<true, bf16>(W, X, (bf16*)Y, M, N, K, ldy, status, glu, stream);
+}
+
+X0NE_API int x0ne_gemm_bf16_tcgen05(const void* W, const void* X, void* Y, int M, int N, int K, int ldy, int out_kind,
+                                    int pair, int* status, cudaStream_t stream) {
+    return x0ne_gemm_bf16_tcgen05_glu(W, X, Y, M, N, K, ldy, out_kind, pair, status, 0.f, 0.f, 0.f, stream);
 }

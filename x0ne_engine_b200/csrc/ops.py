@@ -91,6 +91,9 @@ _SIGNATURES = {
     "x0ne_attention_decode_bf16": [_P, _P, None, _P, _P, _I, _I, _F, _I, _I, _P, _L, _P],
     "x0ne_attention_decode_grouped_bf16": [_P, _P, None, _P, _P, _I, _I, _F, _I, _I, _I, _P, _L, _P],
     "x0ne_gemm_bf16_smallm": [_P, _P, _P, _I, _I, _I, _I, _I, _I, _P],
+    "x0ne_gemm_bf16_smallm_glu": [_P, _P, _P, _I, _I, _I, _I, _I, _I, _F, _F, _F, _P],
+    "x0ne_gemm_bf16_tcgen05_glu": [_P, _P, _P, _I, _I, _I, _I, _I, _I, _P, _F, _F, _F, _P],
+    "x0ne_gemm_bf16_skinny_tcgen05_glu": [_P, _P, _I, _P, _I, _I, _I, _I, _I, _P, _F, _F, _F, _P],
     "x0ne_attention_prefill_tcgen05": [_P, _P, _I, None, _P, _P, _I, _P, _P, _P, _I, _F, _I, _P, _P],
     "x0ne_gemm_bf16_tcgen05": [_P, _P, _P, _I, _I, _I, _I, _I, _I, _P, _P],
     "x0ne_gemm_bf16_skinny_tcgen05": [_P, _P, _I, _P, _I, _I, _I, _I, _I, _P, _P],
@@ -408,7 +411,7 @@ def attention_flex_takes(cache: PagedCacheArg, dtype: torch.dtype, v_from_k: int
     if vd <= 0 or vdp == 0:
         return False
     ks = (max(dkp, vdp) if v_from_k else dkp) + 8
-    tiles = (64 * ks + (0 if v_from_k else 64 * (vdp + 8))) * 2
+    tiles = 2 * (64 * ks + (0 if v_from_k else 64 * (vdp + 8))) * 2        # two stages of a key tile and a value tile
     if decode:
         smem = 16 * ks * 2 + max(tiles, 4 * 16 * (vdp + 2) * 4)
     else:
@@ -649,9 +652,11 @@ def gemm_smallm_takes(w: torch.Tensor, m: int, swiglu: bool = False) -> bool:
     return w.dtype == torch.bfloat16 and 0 < m <= SMALL_M_MAX_ROWS and w.shape[1] % 8 == 0 and not (swiglu and w.shape[0] % 2)
 
 
-def gemm_bf16_smallm(x: torch.Tensor, w: torch.Tensor, y: torch.Tensor, m: int, swiglu: bool = False) -> None:
+def gemm_bf16_smallm(x: torch.Tensor, w: torch.Tensor, y: torch.Tensor, m: int, swiglu: bool = False,
+                     glu: Optional[tuple] = None) -> None:
     """y[:m] = x[:m] @ w.T for m <= 32 by streaming w once; y is bfloat16 or float32.  With
-    `swiglu`, w is the packed [gate; up] weight and y[:m] = silu(x gate^T) * (x up^T)."""
+    `swiglu`, w is the packed [gate; up] weight and y[:m] = silu(x gate^T) * (x up^T); with `glu` =
+    (limit, slope, shift) besides, the clipped unit min(g, limit) sigmoid(slope g) (clamp(u) + shift)."""
     lib = _lib("fast")
     _need(x, torch.bfloat16, "gemm input")
     _need(w, torch.bfloat16, "gemm weight")
@@ -666,6 +671,10 @@ def gemm_bf16_smallm(x: torch.Tensor, w: torch.Tensor, y: torch.Tensor, m: int, 
         kind = 2 if swiglu else 0
     else:
         raise KernelError(f"gemm_smallm: no output kind for {y.dtype} (swiglu={swiglu})")
+    if glu is not None and swiglu:
+        _check(lib, lib.x0ne_gemm_bf16_smallm_glu(_ptr(w), _ptr(x), _ptr(y), m, n, k, n, kind, _sms(w.device),
+                                                  glu[0], glu[1], glu[2], _stream()), "gemm_bf16_smallm")
+        return
     _check(lib, lib.x0ne_gemm_bf16_smallm(_ptr(w), _ptr(x), _ptr(y), m, n, k, n,
                                           kind, _sms(w.device), _stream()), "gemm_bf16_smallm")
 
@@ -713,7 +722,7 @@ def gemm_tc_status(device) -> torch.Tensor:
 
 
 def gemm_bf16_tcgen05(x: torch.Tensor, w: torch.Tensor, y: torch.Tensor, m: int, swiglu: bool = False,
-                      pair: bool = True) -> None:
+                      pair: bool = True, glu: Optional[tuple] = None) -> None:
     """y[:m] = x[:m] @ w.T on the tcgen05 tensor cores (128 x 256 tiles, TMA loads, accumulator in
     tensor memory; with `pair`, pairs of blocks on 256 x 256 tiles); y is bfloat16 or float32.  With `swiglu`, w is the packed [gate; up] weight and
     y[:m] = silu(x gate^T) * (x up^T).  Needs K % 8 == 0."""
@@ -733,6 +742,11 @@ def gemm_bf16_tcgen05(x: torch.Tensor, w: torch.Tensor, y: torch.Tensor, m: int,
         raise KernelError(f"gemm_tc: no output kind for {y.dtype} (swiglu={swiglu})")
     global tc_used
     tc_used = True
+    if glu is not None and swiglu:       # (limit, slope, shift): the clipped gated unit instead of SwiGLU
+        _check(lib, lib.x0ne_gemm_bf16_tcgen05_glu(_ptr(w), _ptr(x), _ptr(y), m, n, k, n, kind, 1 if pair else 0,
+                                                   _ptr(gemm_tc_status(w.device)), glu[0], glu[1], glu[2], _stream()),
+               "gemm_bf16_tcgen05")
+        return
     _check(lib, lib.x0ne_gemm_bf16_tcgen05(_ptr(w), _ptr(x), _ptr(y), m, n, k, n,
                                            kind, 1 if pair else 0, _ptr(gemm_tc_status(w.device)),
                                            _stream()), "gemm_bf16_tcgen05")
@@ -757,7 +771,8 @@ def product_kernel(w: torch.Tensor, m: int, fused: bool = False) -> str:
     return kernel if can else "library"
 
 
-def gemm_bf16_skinny_tcgen05(x: torch.Tensor, w: torch.Tensor, y: torch.Tensor, m: int, swiglu: bool = False) -> None:
+def gemm_bf16_skinny_tcgen05(x: torch.Tensor, w: torch.Tensor, y: torch.Tensor, m: int, swiglu: bool = False,
+                             glu: Optional[tuple] = None) -> None:
     """y[:m] = x[:m] @ w.T for up to 64 rows on tcgen05, K cut over the blocks of a cluster that add
     their partial sums through shared memory; y is bfloat16 or float32.  With `swiglu`, w is the
     packed [gate; up] weight and y[:m] = silu(x gate^T) * (x up^T).  Failures of its bounded waits
@@ -779,6 +794,11 @@ def gemm_bf16_skinny_tcgen05(x: torch.Tensor, w: torch.Tensor, y: torch.Tensor, 
         raise KernelError(f"gemm_skinny_tc: no output kind for {y.dtype} (swiglu={swiglu})")
     tc_used = True
     x_rows = x.numel() // k      # rows really behind x: the copies may read them all (their results are not used)
+    if glu is not None and swiglu:       # (limit, slope, shift): the clipped gated unit instead of SwiGLU
+        _check(lib, lib.x0ne_gemm_bf16_skinny_tcgen05_glu(_ptr(w), _ptr(x), x_rows, _ptr(y), m, n, k, n, kind,
+                                                          _ptr(gemm_tc_status(x.device)), glu[0], glu[1], glu[2], _stream()),
+               "gemm_bf16_skinny_tcgen05")
+        return
     _check(lib, lib.x0ne_gemm_bf16_skinny_tcgen05(_ptr(w), _ptr(x), x_rows, _ptr(y), m, n, k, n, kind,
                                                   _ptr(gemm_tc_status(x.device)), _stream()), "gemm_bf16_skinny_tcgen05")
 

@@ -36,11 +36,11 @@ def run_attention(ctx, q, out, view, n_rows, q_heads, scale, window):
 
 def flex_decode_splits(ctx, n_rows: int, kv_heads: int, q_heads: int, visible: int) -> int:
     """Blocks per (sequence, kv head, 16 q heads) of a decode pass of the general kernel: enough to
-    put two blocks on every multiprocessor, each with at least two pages of the at most `visible`
+    put three blocks on every multiprocessor, each with at least two pages of the at most `visible`
     keys a row reads.  Depends on the pass's numbers only, so a replayed graph keeps it."""
     units = max(1, n_rows * kv_heads * -(-(q_heads // kv_heads) // 16))
     pages = -(-max(1, visible) // 64) + 1
-    return max(1, min(2 * max(1, ctx.sm_count) // units, pages // 2, 32))
+    return max(1, min(3 * max(1, ctx.sm_count) // units, pages // 2, 32))
 
 
 def run_attention_ex(ctx, q, out, view, n_rows, q_heads, scale, window, extra):

@@ -60,8 +60,9 @@ class SwiGLU(FeedForward):
 class ClippedGLU(SwiGLU):
     """down( g sigmoid(slope g) (u + shift) ) with g = min(gate x, limit) and u = clamp(up x, -limit,
     limit): a gated unit whose gate is bounded above and whose linear branch is bounded on both sides
-    and shifted.  One product on the packed [gate; up] weight, the activation in float32, one product
-    with down.  Parameters: hidden_size, intermediate_size, limit, slope, shift, names.{gate, up, down}."""
+    and shifted.  One product on the packed [gate; up] weight, the activation in float32 (in the
+    product's epilogue wherever SwiGLU's is: the same routing table decides), one product with down.
+    Parameters: hidden_size, intermediate_size, limit, slope, shift, names.{gate, up, down}."""
     replayable = True
 
     def __init__(self, spec, env):
@@ -74,8 +75,17 @@ class ClippedGLU(SwiGLU):
         gu = ctx.ws.buffer("ffn.gate_up", (ctx.ws.max_rows, 2 * self.inter), self.env.dtype)
         act = ctx.ws.buffer("ffn.act", (ctx.ws.max_rows, self.inter), self.env.dtype)
         out = ctx.ws.buffer(self.out_buffer, (ctx.ws.max_rows, self.hidden), self.env.dtype)
-        self.gate_up(x, gu, n_rows)
-        ops.glu_clipped(gu, act, n_rows, self.limit, self.slope, self.shift)
+        glu = (self.limit, self.slope, self.shift)
+        kernel = ops.product_kernel(self.gate_up.weight, n_rows, fused=True) if self.env.dtype == torch.bfloat16 else "library"
+        if kernel == "skinny":
+            ops.gemm_bf16_skinny_tcgen05(x, self.gate_up.weight, act, n_rows, swiglu=True, glu=glu)
+        elif kernel == "smallm":
+            ops.gemm_bf16_smallm(x, self.gate_up.weight, act, n_rows, swiglu=True, glu=glu)
+        elif kernel == "tc_pair":
+            ops.gemm_bf16_tcgen05(x, self.gate_up.weight, act, n_rows, swiglu=True, glu=glu)
+        else:
+            self.gate_up(x, gu, n_rows)
+            ops.glu_clipped(gu, act, n_rows, self.limit, self.slope, self.shift)
         self.down(act, out, n_rows)
         return out
 
