@@ -69,7 +69,7 @@ def main(argv=None) -> int:
     ap.add_argument("--dtype", required=True, choices=["bfloat16", "float32"])
     ap.add_argument("--out", required=True, help="folder for <step>.f32 files")
     ap.add_argument("--max-tokens", type=int, required=True,
-                    help="most tokens live requests hold at any time, each rounded up to 64")
+                    help="most tokens live requests hold at any time (the cache adds room for the requests' partly filled pages)")
     ap.add_argument("--device", default="cuda:0")
     ap.add_argument("--max-step-tokens", type=int, default=None,
                     help="most rows the engine runs in one pass; a larger step is cut into several passes "
@@ -86,7 +86,9 @@ def main(argv=None) -> int:
     from ..cache import PAGE_SIZE, pages_for
 
     os.makedirs(args.out, exist_ok=True)
-    capacity = pages_for(args.max_tokens, PAGE_SIZE) * PAGE_SIZE
+    # every live request holds whole pages, so each may waste up to a page less one token beyond its own
+    # tokens: room for 64 such remainders is added to what the caller counted
+    capacity = (pages_for(args.max_tokens, PAGE_SIZE) + 64) * PAGE_SIZE
     engine = Engine.from_folder(args.model, dtype=args.dtype, device=args.device, max_tokens=capacity, max_seq_len=capacity,
                                 max_step_tokens=args.max_step_tokens or min(capacity, 4096))
     print(f"[x0ne-b200] trace_run: {engine.describe()}", file=sys.stderr, flush=True)
