@@ -21,6 +21,9 @@
 #define FX_PAGE 64
 #define FX_TILE_ROWS 128
 #define FX_LOG2E 1.4426950408889634f
+#ifndef FX_DECODE_STAGES
+#define FX_DECODE_STAGES 2      // stages of (key tile, value tile) a decode block copies ahead through
+#endif
 
 __device__ __forceinline__ void fx_mma(float* c, uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
     asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
@@ -90,11 +93,20 @@ __device__ __forceinline__ void fx_load_rows_async(bf16* dst, int stride, const 
         fx_load_rows(dst, stride, src, src_ld, n_rows, r_lo, r_hi, d, dp, tid, nthreads);
         return;
     }
+    // (row, 16-byte piece) of this thread advance by a fixed step: two divisions per call, none per piece
     const int per_row = dp / 8;
-    for (int i = tid; i < n_rows * per_row; i += nthreads) {
-        const int r = i / per_row, c = (i % per_row) * 8;
+    int r = tid / per_row, c8 = tid % per_row;
+    const int dr = nthreads / per_row, dc = nthreads % per_row;
+    while (r < n_rows) {
+        const int c = c8 * 8;
         const bool ok = r >= r_lo && r <= r_hi && c < d;
         fx_cp16(dst + r * stride + c, ok ? src + r * src_ld + c : safe, ok);
+        r += dr;
+        c8 += dc;
+        if (c8 >= per_row) {
+            c8 -= per_row;
+            ++r;
+        }
     }
 }
 
@@ -357,24 +369,25 @@ flex_decode_kernel(const bf16* __restrict__ q, bf16* __restrict__ out, PagedCach
         fx_cp_commit();
         return pb != nullptr;
     };
-    bool have = pg_a <= pg_b ? issue(pg_a, 0) : false;
-    if (pg_a > pg_b) {                       // (no page for this split: only the queries are in flight)
-        fx_cp_commit();
-        fx_cp_wait<0>();
+    // FX_DECODE_STAGES - 1 pages are on their way while one is used; a group is committed for every page
+    // slot, also an empty one, so that "all but the newest FX_DECODE_STAGES - 1 groups" is always this page's
+    unsigned have = 0;                       // bit s: the page in stage s exists
+    for (int i = 0; i < FX_DECODE_STAGES - 1; ++i) {
+        if (pg_a + i <= pg_b) have |= issue(pg_a + i, i) ? 1u << i : 0u;
+        else fx_cp_commit();
     }
     for (int pg = pg_a; pg <= pg_b; ++pg) {
         const int j0 = pg * FX_PAGE;
-        const int stage = (pg - pg_a) & 1;
+        const int stage = (pg - pg_a) % FX_DECODE_STAGES;
         const bf16* ks = ks0 + stage * stage_elems;
         const bf16* vs = ex.v_from_k > 0 ? ks : ks + FX_PAGE * sh.ks;
-        const bool here = have;
-        if (pg < pg_b) {
-            have = issue(pg + 1, stage ^ 1);
-            fx_cp_wait<1>();
-        } else {
-            fx_cp_wait<0>();
-        }
+        const int ahead = pg + FX_DECODE_STAGES - 1, ahead_stage = (ahead - pg_a) % FX_DECODE_STAGES;
+        have &= ~(1u << ahead_stage);        // (that stage was read one page ago; the barrier at that page's end covers it)
+        if (ahead <= pg_b) have |= issue(ahead, ahead_stage) ? 1u << ahead_stage : 0u;
+        else fx_cp_commit();
+        fx_cp_wait<FX_DECODE_STAGES - 1>();
         __syncthreads();
+        const bool here = (have >> stage) & 1u;
         const int jw = j0 + 16 * warp;           // this warp's 16 keys of the page
         if (!here || jw > pos || jw + 16 <= key_lo) {
             __syncthreads();
@@ -421,6 +434,7 @@ flex_decode_kernel(const bf16* __restrict__ q, bf16* __restrict__ out, PagedCach
     l_a += __shfl_xor_sync(0xffffffffu, l_a, 1); l_a += __shfl_xor_sync(0xffffffffu, l_a, 2);
     l_b += __shfl_xor_sync(0xffffffffu, l_b, 1); l_b += __shfl_xor_sync(0xffffffffu, l_b, 2);
     // the four warps' results -> shared memory [warp][item][vdp + 2]
+    fx_cp_wait<0>();
     __syncthreads();
     const int ps = sh.vdp + 2;
     {
@@ -474,8 +488,9 @@ flex_decode_kernel(const bf16* __restrict__ q, bf16* __restrict__ out, PagedCach
 }
 
 // Merges the splits of every unit in split order and writes the rows out.  One block of 256 threads per
-// unit: 16 threads per item (q head), each with every 16th column; the splits' weights 2^(m_s - m) are
-// worked out once per item and kept in shared memory.
+// unit.  First a warp per item (q head) reads the splits' maxima and sums, one split per lane, and leaves
+// the splits' weights 2^(m_s - m) and the item's final factor (1 / sum, sink, gate) in shared memory; then
+// the threads share the (item, column) pairs and add the splits up in split order.
 #define FX_MAX_SPLITS 64
 __global__ void __launch_bounds__(256)
 flex_decode_merge_kernel(const float* __restrict__ scratch, bf16* __restrict__ out, int q_heads, int kv_heads,
@@ -483,43 +498,46 @@ flex_decode_merge_kernel(const float* __restrict__ scratch, bf16* __restrict__ o
     __shared__ float wgt[16][FX_MAX_SPLITS];
     __shared__ float fin_s[16];
     pdl_prologue();
-    const int unit = blockIdx.x, tid = threadIdx.x;
+    const int unit = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int group = q_heads / kv_heads;
     const int chunk_i = unit % chunks, kh = (unit / chunks) % kv_heads, row = unit / (chunks * kv_heads);
     const int head0 = kh * group + chunk_i * 16, n_items = min(16, group - chunk_i * 16);
-    const int item = tid >> 4, c0 = tid & 15, ps = vdp + 2;
-    const float* src = scratch + ((int64_t)unit * splits * 16 + item) * ps;
+    const int ps = vdp + 2;
+    const float* base = scratch + (int64_t)unit * splits * 16 * ps;
     const int64_t step = (int64_t)16 * ps;
-    if (c0 == 0 && item < n_items) {
-        float mm = -INFINITY;
-        for (int s = 0; s < splits; ++s) mm = fmaxf(mm, src[s * step]);
+    for (int item = warp; item < n_items; item += 8) {
+        const float* src = base + (int64_t)item * ps;
+        const int s0 = lane, s1 = lane + 32;
+        const float m0 = s0 < splits ? src[s0 * step] : -INFINITY, m1 = s1 < splits ? src[s1 * step] : -INFINITY;
+        const float l0 = s0 < splits ? src[s0 * step + 1] : 0.f, l1 = s1 < splits ? src[s1 * step + 1] : 0.f;
+        const float mm = warp_max(fmaxf(m0, m1));
         const float ref = mm == -INFINITY ? 0.f : mm;
-        float ll = 0.f;
-        for (int s = 0; s < splits; ++s) {
-            const float f = exp2f(src[s * step] - ref);
-            wgt[item][s] = f;
-            ll += src[s * step + 1] * f;
+        const float f0 = exp2f(m0 - ref), f1 = exp2f(m1 - ref);
+        if (s0 < splits) wgt[item][s0] = f0;
+        if (s1 < splits) wgt[item][s1] = f1;
+        float ll = warp_sum(l0 * f0 + l1 * f1);      // (a fixed tree over the lanes: the same bits on every call)
+        if (lane == 0) {
+            const int head = head0 + item;
+            float fin = 1.f;
+            if (ex.sink != nullptr) {
+                const float sink2 = ex.sink[head] * FX_LOG2E;
+                const float mf = fmaxf(mm, sink2);
+                fin = exp2f(mm - mf);
+                ll = ll * fin + exp2f(sink2 - mf);
+            }
+            fin *= ll > 0.f ? 1.0f / ll : 0.f;
+            if (ex.gate != nullptr) fin *= 1.0f / (1.0f + expf(-__bfloat162float(((const bf16*)ex.gate)[(int64_t)row * ex.gate_ld + head])));
+            fin_s[item] = fin;
         }
-        const int head = head0 + item;
-        float fin = 1.f;
-        if (ex.sink != nullptr) {
-            const float sink2 = ex.sink[head] * FX_LOG2E;
-            const float mf = fmaxf(mm, sink2);
-            fin = exp2f(mm - mf);
-            ll = ll * fin + exp2f(sink2 - mf);
-        }
-        fin *= ll > 0.f ? 1.0f / ll : 0.f;
-        if (ex.gate != nullptr) fin *= 1.0f / (1.0f + expf(-__bfloat162float(((const bf16*)ex.gate)[(int64_t)row * ex.gate_ld + head])));
-        fin_s[item] = fin;
     }
     __syncthreads();
-    if (item >= n_items) return;
-    const float fin = fin_s[item];
-    bf16* orow = out + ((int64_t)row * q_heads + head0 + item) * vd;
-    for (int c = c0; c < vd; c += 16) {
+    bf16* orow = out + ((int64_t)row * q_heads + head0) * vd;
+    for (int i = tid; i < n_items * vd; i += 256) {
+        const int item = i / vd, c = i - item * vd;
+        const float* src = base + (int64_t)item * ps + 2 + c;
         float acc = 0.f;
-        for (int s = 0; s < splits; ++s) acc += src[s * step + 2 + c] * wgt[item][s];
-        orow[c] = __float2bfloat16_rn(acc * fin);
+        for (int s = 0; s < splits; ++s) acc += src[s * step] * wgt[item][s];
+        orow[i] = __float2bfloat16_rn(acc * fin_s[item]);
     }
 }
 
@@ -558,7 +576,7 @@ static size_t fx_prefill_smem(const FxShape& sh, bool v_from_k) {
     return ((size_t)(FX_TILE_ROWS + 2 * FX_PAGE) * sh.ks + (v_from_k ? 0 : (size_t)2 * FX_PAGE * sh.vs)) * sizeof(bf16);
 }
 static size_t fx_decode_smem(const FxShape& sh, bool v_from_k) {
-    const size_t tiles = 2 * ((size_t)FX_PAGE * sh.ks + (v_from_k ? 0 : (size_t)FX_PAGE * sh.vs)) * sizeof(bf16);
+    const size_t tiles = FX_DECODE_STAGES * ((size_t)FX_PAGE * sh.ks + (v_from_k ? 0 : (size_t)FX_PAGE * sh.vs)) * sizeof(bf16);
     const size_t merge = (size_t)4 * 16 * (sh.vdp + 2) * sizeof(float);
     return (size_t)16 * sh.ks * sizeof(bf16) + (tiles > merge ? tiles : merge);
 }

@@ -82,6 +82,38 @@ X0NE_API int x0ne_glu_clipped(const void* gate_up, void* out, int dt, int n_rows
     X0NE_LAUNCH_CHECK();
 }
 
+// 8 consecutive values as 16-byte (bfloat16) or 2 x 16-byte (float) accesses
+__device__ __forceinline__ void copy8(bf16* d, const bf16* s) { *reinterpret_cast<uint4*>(d) = *reinterpret_cast<const uint4*>(s); }
+__device__ __forceinline__ void copy8(float* d, const float* s) {
+    reinterpret_cast<float4*>(d)[0] = reinterpret_cast<const float4*>(s)[0];
+    reinterpret_cast<float4*>(d)[1] = reinterpret_cast<const float4*>(s)[1];
+}
+__device__ __forceinline__ void load8f(const bf16* p, float* v) {
+    const uint4 u = *reinterpret_cast<const uint4*>(p);
+    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&u);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const float2 f = __bfloat1622float2(h[i]);
+        v[2 * i] = f.x;
+        v[2 * i + 1] = f.y;
+    }
+}
+__device__ __forceinline__ void load8f(const float* p, float* v) {
+    const float4 a = reinterpret_cast<const float4*>(p)[0], b = reinterpret_cast<const float4*>(p)[1];
+    v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+}
+__device__ __forceinline__ void store8f(bf16* p, const float* v) {
+    uint4 u;
+    __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&u);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) h[i] = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
+    *reinterpret_cast<uint4*>(p) = u;
+}
+__device__ __forceinline__ void store8f(float* p, const float* v) {
+    reinterpret_cast<float4*>(p)[0] = make_float4(v[0], v[1], v[2], v[3]);
+    reinterpret_cast<float4*>(p)[1] = make_float4(v[4], v[5], v[6], v[7]);
+}
+
 // ----------------------------------------------------------------------------------------
 // K/V write of an attention without rotation.  `src` holds, per row of `ld` values, the keys at
 // column k_col (kv_heads x k_dim) and the values at column v_col (kv_heads x v_dim).
@@ -95,7 +127,7 @@ X0NE_API int x0ne_glu_clipped(const void* gate_up, void* out, int dt, int n_rows
 template <typename T>
 __global__ void kv_write_blend_kernel(const T* __restrict__ src, int ld, int k_col, int v_col, T* __restrict__ v_first,
                                       const float* __restrict__ lambda, int mode, PagedCache cache,
-                                      const int32_t* __restrict__ row_slot, const int32_t* __restrict__ row_pos) {
+                                      const int32_t* __restrict__ row_slot, const int32_t* __restrict__ row_pos, int vec) {
     pdl_launch_dependents();
     const float lam = mode == 2 ? lambda[0] : 0.f;
     const int row = blockIdx.x;
@@ -106,6 +138,31 @@ __global__ void kv_write_blend_kernel(const T* __restrict__ src, int ld, int k_c
     const T* s = src + (int64_t)row * ld;
     const int64_t k0 = cache_row_offset(cache, slot, pos, 0, 0);
     const int64_t head_k = (int64_t)cache.page_size * kd, head_v = (int64_t)cache.page_size * vd;
+    if (vec) {
+        // 8 values at a time (16 bytes of bfloat16): every width and column is a multiple of 8 and the rows are aligned
+        const int64_t v0 = cache_row_offset(cache, slot, pos, 0, 1);
+        const int nk = kvh * kd / 8, nv = kvh * vd / 8;
+        for (int i = threadIdx.x; i < nk + nv; i += blockDim.x) {
+            if (i < nk) {
+                const int e = i * 8;
+                if (k0 >= 0) copy8(base + k0 + (e / kd) * head_k + (e % kd), s + k_col + e);
+                continue;
+            }
+            const int e = (i - nk) * 8;
+            float v[8];
+            load8f(s + v_col + e, v);
+            T* first = v_first + (int64_t)row * kvh * vd + e;
+            if (mode == 1) copy8(first, s + v_col + e);
+            if (mode == 2) {
+                float f[8];
+                load8f(first, f);
+#pragma unroll
+                for (int k = 0; k < 8; ++k) v[k] = (1.0f - lam) * v[k] + lam * f[k];
+            }
+            if (v0 >= 0) store8f(base + v0 + (e / vd) * head_v + (e % vd), v);
+        }
+        return;
+    }
     if (k0 >= 0)
         for (int i = threadIdx.x; i < kvh * kd; i += blockDim.x) base[k0 + (i / kd) * head_k + (i % kd)] = s[k_col + i];
     const int64_t v0 = cache_row_offset(cache, slot, pos, 0, 1);
@@ -127,10 +184,13 @@ X0NE_API int x0ne_kv_write_blend(const void* src, int dt, int ld, int k_col, int
     X0NE_REQUIRE(mode == 0 || v_first != nullptr, "kv_write: mode %d needs the buffer of first values", mode);
     X0NE_REQUIRE(mode != 2 || lambda != nullptr, "kv_write: blending needs its weight");
     if (n_rows == 0) return 0;
+    const int vd = cache_v_dim(cache);
+    const int vec = (cache.head_dim % 8 == 0 && vd % 8 == 0 && ld % 8 == 0 && k_col % 8 == 0 && v_col % 8 == 0 &&
+                     ((((uintptr_t)src | (uintptr_t)v_first | (uintptr_t)cache.base) & 31) == 0) && cache.page_stride % 8 == 0) ? 1 : 0;
     if (dt == X0NE_F32)
-        x0ne_launch(kv_write_blend_kernel<float>, dim3(n_rows), dim3(128), 0, stream, (const float*)src, ld, k_col, v_col, (float*)v_first, lambda, mode, cache, row_slot, row_pos);
+        x0ne_launch(kv_write_blend_kernel<float>, dim3(n_rows), dim3(128), 0, stream, (const float*)src, ld, k_col, v_col, (float*)v_first, lambda, mode, cache, row_slot, row_pos, vec);
     else if (dt == X0NE_BF16)
-        x0ne_launch(kv_write_blend_kernel<bf16>, dim3(n_rows), dim3(128), 0, stream, (const bf16*)src, ld, k_col, v_col, (bf16*)v_first, lambda, mode, cache, row_slot, row_pos);
+        x0ne_launch(kv_write_blend_kernel<bf16>, dim3(n_rows), dim3(128), 0, stream, (const bf16*)src, ld, k_col, v_col, (bf16*)v_first, lambda, mode, cache, row_slot, row_pos, vec);
     else
         X0NE_REQUIRE(false, "kv_write: unknown dtype tag %d", dt);
     X0NE_LAUNCH_CHECK();
@@ -193,9 +253,17 @@ __global__ void latent_prepare_kernel(const T* __restrict__ src, int ld, int dkv
     }
     const int qw = rank + rot;
     T* qo = q_out + (int64_t)row * heads * qw;
-    for (int i = threadIdx.x; i < heads * rank; i += blockDim.x) {
-        const int h = i / rank, d = i % rank;
-        qo[h * qw + d] = q_abs[h * q_abs_head_stride + (int64_t)row * rank + d];
+    if (rank % 8 == 0 && qw % 8 == 0 && q_abs_head_stride % 8 == 0 && ((((uintptr_t)q_out | (uintptr_t)q_abs) & 31) == 0)) {
+        const int per_head = rank / 8;
+        for (int i = threadIdx.x; i < heads * per_head; i += blockDim.x) {
+            const int h = i / per_head, d = (i - h * per_head) * 8;
+            copy8(qo + h * qw + d, q_abs + h * q_abs_head_stride + (int64_t)row * rank + d);
+        }
+    } else {
+        for (int i = threadIdx.x; i < heads * rank; i += blockDim.x) {
+            const int h = i / rank, d = i % rank;
+            qo[h * qw + d] = q_abs[h * q_abs_head_stride + (int64_t)row * rank + d];
+        }
     }
     for (int i = threadIdx.x; i < heads * half; i += blockDim.x) {
         const int h = i / half, j = i % half;

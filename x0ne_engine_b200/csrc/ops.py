@@ -411,9 +411,10 @@ def attention_flex_takes(cache: PagedCacheArg, dtype: torch.dtype, v_from_k: int
     if vd <= 0 or vdp == 0:
         return False
     ks = (max(dkp, vdp) if v_from_k else dkp) + 8
-    tiles = 2 * (64 * ks + (0 if v_from_k else 64 * (vdp + 8))) * 2        # two stages of a key tile and a value tile
+    stage = (64 * ks + (0 if v_from_k else 64 * (vdp + 8))) * 2        # a key tile and a value tile
+    tiles = 2 * stage
     if decode:
-        smem = 16 * ks * 2 + max(tiles, 4 * 16 * (vdp + 2) * 4)
+        smem = 16 * ks * 2 + max(2 * stage, 4 * 16 * (vdp + 2) * 4)
     else:
         smem = 128 * ks * 2 + tiles
     return smem <= FLEX_SMEM_LIMIT

@@ -34,13 +34,36 @@ def run_attention(ctx, q, out, view, n_rows, q_heads, scale, window):
                q_heads, scale, window)
 
 
+FLEX_DECODE_BLOCKS_PER_SM = 3      # blocks of the general decode kernel a multiprocessor holds at width 128
+FLEX_DECODE_FIXED_PAGES = 4        # what a block costs besides walking its pages, in pages' worth of time
+FLEX_DECODE_MAX_WAVES = 8          # several splits are taken only while the launch stays within so many waves of blocks
+
+
 def flex_decode_splits(ctx, n_rows: int, kv_heads: int, q_heads: int, visible: int) -> int:
-    """Blocks per (sequence, kv head, 16 q heads) of a decode pass of the general kernel: enough to
-    put three blocks on every multiprocessor, each with at least two pages of the at most `visible`
-    keys a row reads.  Depends on the pass's numbers only, so a replayed graph keeps it."""
+    """Blocks per (sequence, kv head, 16 q heads) of a decode pass of the general kernel.  A launch of
+    units x splits blocks runs in ceil(blocks / resident) waves, each as long as a block's walk over
+    pages / splits pages plus a fixed cost; the split with the shortest total wins (measured at batch 8,
+    3,072 keys: 6 splits, one full wave, 33.9 us against 45.2 with 4 and 46.5 with 9; at batch 64 two
+    splits 204 us against 240 with one).  Depends on the pass's numbers only, so a replayed graph keeps it."""
     units = max(1, n_rows * kv_heads * -(-(q_heads // kv_heads) // 16))
     pages = -(-max(1, visible) // 64) + 1
-    return max(1, min(3 * max(1, ctx.sm_count) // units, pages // 2, 32))
+    resident = FLEX_DECODE_BLOCKS_PER_SM * max(1, ctx.sm_count)
+    best, best_cost = 1, None
+    for splits in range(1, max(1, min(pages // 2, 32)) + 1):
+        waves = -(-units * splits // resident)
+        if splits > 1 and waves > FLEX_DECODE_MAX_WAVES:
+            break
+        cost = waves * (pages / splits + FLEX_DECODE_FIXED_PAGES)
+        if best_cost is None or cost < best_cost - 1e-9:
+            best, best_cost = splits, cost
+    return best
+
+
+def flex_decode_scratch_floats(ctx, vd: int) -> int:
+    """Scratch of the largest launch flex_decode_splits gives several splits: one size, so that a
+    captured graph's pointer stays good."""
+    blocks = FLEX_DECODE_MAX_WAVES * FLEX_DECODE_BLOCKS_PER_SM * max(1, ctx.sm_count)
+    return blocks * 16 * (ops.flex_value_bucket(vd) + 2)
 
 
 def run_attention_ex(ctx, q, out, view, n_rows, q_heads, scale, window, extra):
@@ -55,8 +78,8 @@ def run_attention_ex(ctx, q, out, view, n_rows, q_heads, scale, window, extra):
         scratch = None
         if splits > 1:
             vd = extra.v_from_k or view.value_dim
-            scratch = ctx.ws.buffer("attn.flex_parts", (ops.attention_flex_scratch_bytes(ctx.ws.max_rows, q_heads, view.kv_heads, vd, 32) // 4,),
-                                    torch.float32)
+            scratch = ctx.ws.buffer("attn.flex_parts", (max(flex_decode_scratch_floats(ctx, vd), ops.attention_flex_scratch_bytes(
+                n_rows, q_heads, view.kv_heads, vd, splits) // 4),), torch.float32)
         ops.attention_flex_decode(q, out, view, ctx.row_slot, ctx.row_pos, n_rows, q_heads, scale, window, extra, splits, scratch)
     else:
         ops.attention_flex_prefill(q, out, view, ctx.tile_seq, ctx.tile_row0, ctx.n_tiles, ctx.seq_first_row, ctx.seq_slot,
