@@ -440,3 +440,17 @@ def test_clipped_unit_in_the_products_epilogues(rows, inter, k):
         assert err <= 2 ** -7 * want.abs().max().item(), f"{name}: {err}"
         ran += 1
     assert ran >= 1
+
+
+def test_bfloat16_falls_back_to_the_plain_kernel_where_the_general_ones_do_not_take_a_shape(monkeypatch):
+    """Values wider than the tensor-core kernels are compiled for go to the plain kernel, in bfloat16 too:
+    forced here for every layer of a small model, prompts and decoding."""
+    from x0ne_engine_b200 import Engine
+    from x0ne_engine_b200.csrc import ops
+    folder, cfg, t = H.folder("mixed")
+    eng = Engine.from_folder(folder, dtype="bfloat16", max_tokens=512, max_seq_len=512)
+    monkeypatch.setattr(ops, "attention_flex_takes", lambda *a, **k: False)
+    ids = ids_for(cfg, 90, seed=31)
+    want = H.plain_logits(cfg, t, ids)
+    check("bfloat16", whole(eng, ids), want, "plain kernel, prompt")
+    check("bfloat16", in_pieces(eng, ids, [70] + [1] * 20), want, "plain kernel, decoded")
