@@ -55,10 +55,9 @@ __device__ __forceinline__ uint32_t fx_pack(float lo, float hi) {
 }
 // bfloat16(p) and the bfloat16 of what that rounding lost, for two weights at once
 __device__ __forceinline__ void fx_split(float p0, float p1, uint32_t& hi, uint32_t& lo) {
-    const __nv_bfloat16 h0 = __float2bfloat16_rn(p0), h1 = __float2bfloat16_rn(p1);
-    const __nv_bfloat162 hv = __halves2bfloat162(h0, h1);
+    const __nv_bfloat162 hv = __floats2bfloat162_rn(p0, p1);          // p0 in the low half
     hi = *reinterpret_cast<const uint32_t*>(&hv);
-    lo = fx_pack(p0 - __bfloat162float(h0), p1 - __bfloat162float(h1));
+    lo = fx_pack(p0 - __uint_as_float(hi << 16), p1 - __uint_as_float(hi & 0xffff0000u));
 }
 
 // Copies rows [0, n_rows) of `d` values (row r at src + r * src_ld) into dst rows of `stride` values,
@@ -212,6 +211,9 @@ flex_prefill_kernel(const bf16* __restrict__ q, bf16* __restrict__ out, PagedCac
     const bool ok_a = r_a < n_rows, ok_b = r_b < n_rows;
     const int warp_last = pos0 + min(warp * 16 + 15, n_rows - 1);  // the largest position a row of this warp has
     const int warp_first_key = fx_first_key(pos0 + warp * 16, window, ex.chunk);   // first keys only grow along the rows
+    const bool warp_all_rows = warp * 16 + 15 < n_rows;
+    const int warp_first_pos = pos0 + warp * 16;                                    // the smallest position of this warp's rows
+    const int warp_last_key = fx_first_key(pos0 + warp * 16 + 15, window, ex.chunk);   // the largest first key of them
     float m_a = -INFINITY, m_b = -INFINITY, l_a = 0.f, l_b = 0.f;
     float o[DVT][4];
 #pragma unroll
@@ -253,15 +255,26 @@ flex_prefill_kernel(const bf16* __restrict__ q, bf16* __restrict__ out, PagedCac
         float s[8][4];
         fx_scores<8>(s, qs + warp * 16 * sh.ks, ks, sh.ks, sh.dkp, 0, lane);
         float mx_a = -INFINITY, mx_b = -INFINITY;
+        if (warp_all_rows && j0 + FX_PAGE - 1 <= warp_first_pos && j0 >= warp_last_key) {
+            // every key of the page is seen by every row of this warp: no comparisons
 #pragma unroll
-        for (int n = 0; n < 8; ++n) {
+            for (int n = 0; n < 8; ++n) {
 #pragma unroll
-            for (int e = 0; e < 2; ++e) {
-                const int j = j0 + 8 * n + 2 * t + e;
-                s[n][e] = (ok_a && j <= pos_a && j >= lo_a) ? s[n][e] * sc2 : -INFINITY;
-                s[n][2 + e] = (ok_b && j <= pos_b && j >= lo_b) ? s[n][2 + e] * sc2 : -INFINITY;
-                mx_a = fmaxf(mx_a, s[n][e]);
-                mx_b = fmaxf(mx_b, s[n][2 + e]);
+                for (int e = 0; e < 4; ++e) s[n][e] *= sc2;
+                mx_a = fmaxf(mx_a, fmaxf(s[n][0], s[n][1]));
+                mx_b = fmaxf(mx_b, fmaxf(s[n][2], s[n][3]));
+            }
+        } else {
+#pragma unroll
+            for (int n = 0; n < 8; ++n) {
+#pragma unroll
+                for (int e = 0; e < 2; ++e) {
+                    const int j = j0 + 8 * n + 2 * t + e;
+                    s[n][e] = (ok_a && j <= pos_a && j >= lo_a) ? s[n][e] * sc2 : -INFINITY;
+                    s[n][2 + e] = (ok_b && j <= pos_b && j >= lo_b) ? s[n][2 + e] * sc2 : -INFINITY;
+                    mx_a = fmaxf(mx_a, s[n][e]);
+                    mx_b = fmaxf(mx_b, s[n][2 + e]);
+                }
             }
         }
         mx_a = fmaxf(mx_a, __shfl_xor_sync(0xffffffffu, mx_a, 1));
@@ -283,8 +296,10 @@ flex_prefill_kernel(const bf16* __restrict__ q, bf16* __restrict__ out, PagedCac
         l_b = l_b * al_b + sum_b;
         m_a = mn_a;
         m_b = mn_b;
+        if (!__all_sync(0xffffffffu, al_a == 1.f && al_b == 1.f)) {      // (once the maxima have settled nothing is rescaled)
 #pragma unroll
-        for (int n = 0; n < DVT; ++n) { o[n][0] *= al_a; o[n][1] *= al_a; o[n][2] *= al_b; o[n][3] *= al_b; }
+            for (int n = 0; n < DVT; ++n) { o[n][0] *= al_a; o[n][1] *= al_a; o[n][2] *= al_b; o[n][3] *= al_b; }
+        }
         fx_accumulate<DVT, 4>(o, s, vs, vstride, 0, lane);
         __syncthreads();          // every warp is done with this stage before the page after next is copied into it
     }
@@ -426,8 +441,10 @@ flex_decode_kernel(const bf16* __restrict__ q, bf16* __restrict__ out, PagedCach
         l_b = l_b * al_b + sum_b;
         m_a = mn_a;
         m_b = mn_b;
+        if (!__all_sync(0xffffffffu, al_a == 1.f && al_b == 1.f)) {      // (once the maxima have settled nothing is rescaled)
 #pragma unroll
-        for (int n = 0; n < DVT; ++n) { o[n][0] *= al_a; o[n][1] *= al_a; o[n][2] *= al_b; o[n][3] *= al_b; }
+            for (int n = 0; n < DVT; ++n) { o[n][0] *= al_a; o[n][1] *= al_a; o[n][2] *= al_b; o[n][3] *= al_b; }
+        }
         fx_accumulate<DVT, 1>(o, s, vs, vstride, 16 * warp, lane);
         __syncthreads();
     }
