@@ -78,7 +78,7 @@ def test_cache_pages_with_other_value_widths():
 
 
 @pytest.mark.parametrize("dims,base,scaling", [(6, 10000.0, {"factor": 8.0, "original": 64, "fast": 16.0, "slow": 2.0}),
-                                               (16, 500000.0, {"factor": 4.0, "original": 512, "fast": 32.0, "slow": 1.0}),
+                                               (24, 250000.0, {"factor": 6.0, "original": 2048, "fast": 24.0, "slow": 1.5}),
                                                (32, 1e6, {"factor": 40.0, "original": 4096, "fast": 32.0, "slow": 1.0}),
                                                (8, 100.0, None)])
 def test_rotary_frequencies_against_the_plain_formula(dims, base, scaling):
