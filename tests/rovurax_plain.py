@@ -20,10 +20,6 @@ def rms_norm(x: torch.Tensor, w: torch.Tensor, eps: float) -> torch.Tensor:
     return x / torch.sqrt((x * x).mean(-1, keepdim=True) + eps) * w
 
 
-def gelu_tanh(z: torch.Tensor) -> torch.Tensor:
-    return 0.5 * z * (1.0 + torch.tanh(math.sqrt(2.0 / math.pi) * (z + 0.044715 * z ** 3)))
-
-
 def clipped_glu(h: torch.Tensor, gate: torch.Tensor, up: torch.Tensor, down: torch.Tensor, limit: float) -> torch.Tensor:
     """g = min(gate h, L); u = clamp(up h, -L, L); down (g sigmoid(1.702 g) (u + 1))."""
     g = torch.clamp(h @ gate.T, max=limit)
