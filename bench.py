@@ -12,6 +12,12 @@ time); `e2e` is the same rate through `Model.generate` with host token lists in 
 `prefill` is one 2,048-token prompt through the step function; `points` has decode at batch 1
 and 64 and the milliseconds a 128-token and a 512-token prompt take through the step function; `roofline` places the decode step against the bytes it must read.  One JSON line is
 printed.  This library runs on one GPU: for --gpus above 1 a line says so and the exit code is 2.
+
+    python bench.py --design rovurax [--sizes 1.7b,8b] [--layers 8] [--chunk 1024] [--steps K]
+
+instead runs the Rovurax design beside Qwen3 at equal sizes (random bfloat16 weights, the same engine,
+step function and decode graphs): one prompt of --prefill-tokens through the step function, then decode
+at --batch, device-timed; one JSON line with a row per size and design.
 """
 from __future__ import annotations
 

@@ -454,3 +454,9 @@ def test_bfloat16_falls_back_to_the_plain_kernel_where_the_general_ones_do_not_t
     want = H.plain_logits(cfg, t, ids)
     check("bfloat16", whole(eng, ids), want, "plain kernel, prompt")
     check("bfloat16", in_pieces(eng, ids, [70] + [1] * 20), want, "plain kernel, decoded")
+
+
+def test_the_tile_height_the_engine_plans_with_is_the_kernels_own():
+    from x0ne_engine_b200.csrc import ops
+    assert ops.attention_prefill_tile_rows() == ops.PREFILL_TILE_ROWS
+    assert int(ops._lib("flex").x0ne_attention_flex_tile_rows()) == ops.PREFILL_TILE_ROWS
