@@ -83,27 +83,39 @@ __device__ __forceinline__ void fx_load_rows(bf16* dst, int stride, const bf16* 
     }
 }
 
+// Where a thread starts and how it steps when a block shares the 16-byte pieces of a tile's rows: worked
+// out once per kernel (the divisions), used for every page.
+struct FxPieces {
+    int r0, c0, dr, dc, per_row;
+};
+__device__ __forceinline__ FxPieces fx_pieces(int dp, int tid, int nthreads) {
+    FxPieces p;
+    p.per_row = dp / 8;
+    p.r0 = tid / p.per_row;
+    p.c0 = tid % p.per_row;
+    p.dr = nthreads / p.per_row;
+    p.dc = nthreads % p.per_row;
+    return p;
+}
+
 // The same through cp.async where rows can be copied 16 bytes at a time (the caller commits and waits);
 // other shapes, and a missing source, are written with plain stores.  `safe` is any address of global memory.
 __device__ __forceinline__ void fx_load_rows_async(bf16* dst, int stride, const bf16* src, int64_t src_ld, int n_rows, int r_lo, int r_hi,
-                                                   int d, int dp, int tid, int nthreads, const bf16* safe) {
+                                                   int d, int dp, int tid, int nthreads, const bf16* safe, const FxPieces& pc) {
     const bool vec = src != nullptr && (d % 8 == 0) && (src_ld % 8 == 0) && ((((uintptr_t)src) & 15) == 0);
     if (!vec) {
         fx_load_rows(dst, stride, src, src_ld, n_rows, r_lo, r_hi, d, dp, tid, nthreads);
         return;
     }
-    // (row, 16-byte piece) of this thread advance by a fixed step: two divisions per call, none per piece
-    const int per_row = dp / 8;
-    int r = tid / per_row, c8 = tid % per_row;
-    const int dr = nthreads / per_row, dc = nthreads % per_row;
+    int r = pc.r0, c8 = pc.c0;
     while (r < n_rows) {
         const int c = c8 * 8;
         const bool ok = r >= r_lo && r <= r_hi && c < d;
         fx_cp16(dst + r * stride + c, ok ? src + r * src_ld + c : safe, ok);
-        r += dr;
-        c8 += dc;
-        if (c8 >= per_row) {
-            c8 -= per_row;
+        r += pc.dr;
+        c8 += pc.dc;
+        if (c8 >= pc.per_row) {
+            c8 -= pc.per_row;
             ++r;
         }
     }
@@ -202,7 +214,8 @@ flex_prefill_kernel(const bf16* __restrict__ q, bf16* __restrict__ out, PagedCac
     pdl_wait();
     const int64_t q_ld = ex.q_ld > 0 ? ex.q_ld : (int64_t)q_heads * sh.dk;
     const bf16* safe = (const bf16*)cache.base;
-    fx_load_rows_async(qs, sh.ks, q + (int64_t)row0 * q_ld + (int64_t)head * sh.dk, q_ld, FX_TILE_ROWS, 0, n_rows - 1, sh.dk, sh.dkp, tid, 256, safe);
+    const FxPieces pk = fx_pieces(sh.dkp, tid, 256), pv = fx_pieces(sh.vdp, tid, 256);
+    fx_load_rows_async(qs, sh.ks, q + (int64_t)row0 * q_ld + (int64_t)head * sh.dk, q_ld, FX_TILE_ROWS, 0, n_rows - 1, sh.dk, sh.dkp, tid, 256, safe, pk);
 
     const float sc2 = scale * FX_LOG2E;
     const int r_a = warp * 16 + g, r_b = r_a + 8;                  // this thread's two rows of the tile
@@ -227,9 +240,9 @@ flex_prefill_kernel(const bf16* __restrict__ q, bf16* __restrict__ out, PagedCac
         const int page = fx_page(cache, slot, pg);
         const bf16* pb = page >= 0 ? (const bf16*)cache.base + (int64_t)page * cache.page_stride : nullptr;
         bf16* kd = ks0 + stage * stage_elems;
-        fx_load_rows_async(kd, sh.ks, pb ? pb + k_head : nullptr, sh.dk, FX_PAGE, 0, key_hi - pg * FX_PAGE, sh.dk, sh.dkp, tid, 256, safe);
+        fx_load_rows_async(kd, sh.ks, pb ? pb + k_head : nullptr, sh.dk, FX_PAGE, 0, key_hi - pg * FX_PAGE, sh.dk, sh.dkp, tid, 256, safe, pk);
         if (ex.v_from_k <= 0)
-            fx_load_rows_async(kd + FX_PAGE * sh.ks, sh.vs, pb ? pb + v_head : nullptr, sh.vd, FX_PAGE, 0, key_hi - pg * FX_PAGE, sh.vd, sh.vdp, tid, 256, safe);
+            fx_load_rows_async(kd + FX_PAGE * sh.ks, sh.vs, pb ? pb + v_head : nullptr, sh.vd, FX_PAGE, 0, key_hi - pg * FX_PAGE, sh.vd, sh.vdp, tid, 256, safe, pv);
         fx_cp_commit();
         return pb != nullptr;
     };
@@ -361,7 +374,8 @@ flex_decode_kernel(const bf16* __restrict__ q, bf16* __restrict__ out, PagedCach
     pdl_wait();
     const int64_t q_ld = ex.q_ld > 0 ? ex.q_ld : (int64_t)q_heads * sh.dk;
     const bf16* safe = (const bf16*)cache.base;
-    fx_load_rows_async(qs, sh.ks, q + (int64_t)row * q_ld + (int64_t)head0 * sh.dk, sh.dk, 16, 0, n_items - 1, sh.dk, sh.dkp, tid, 128, safe);
+    const FxPieces pk = fx_pieces(sh.dkp, tid, 128), pv = fx_pieces(sh.vdp, tid, 128);
+    fx_load_rows_async(qs, sh.ks, q + (int64_t)row * q_ld + (int64_t)head0 * sh.dk, sh.dk, 16, 0, n_items - 1, sh.dk, sh.dkp, tid, 128, safe, pk);
 
     const float sc2 = scale * FX_LOG2E;
     const int key_lo = fx_first_key(pos, window, ex.chunk);
@@ -378,9 +392,9 @@ flex_decode_kernel(const bf16* __restrict__ q, bf16* __restrict__ out, PagedCach
         const int page = fx_page(cache, slot, pg);
         const bf16* pb = page >= 0 ? (const bf16*)cache.base + (int64_t)page * cache.page_stride : nullptr;
         bf16* kd = ks0 + stage * stage_elems;
-        fx_load_rows_async(kd, sh.ks, pb ? pb + k_head : nullptr, sh.dk, FX_PAGE, 0, pos - pg * FX_PAGE, sh.dk, sh.dkp, tid, 128, safe);
+        fx_load_rows_async(kd, sh.ks, pb ? pb + k_head : nullptr, sh.dk, FX_PAGE, 0, pos - pg * FX_PAGE, sh.dk, sh.dkp, tid, 128, safe, pk);
         if (ex.v_from_k <= 0)
-            fx_load_rows_async(kd + FX_PAGE * sh.ks, sh.vs, pb ? pb + v_head : nullptr, sh.vd, FX_PAGE, 0, pos - pg * FX_PAGE, sh.vd, sh.vdp, tid, 128, safe);
+            fx_load_rows_async(kd + FX_PAGE * sh.ks, sh.vs, pb ? pb + v_head : nullptr, sh.vd, FX_PAGE, 0, pos - pg * FX_PAGE, sh.vd, sh.vdp, tid, 128, safe, pv);
         fx_cp_commit();
         return pb != nullptr;
     };
