@@ -50,6 +50,10 @@ CONFIGS = {
     # many q heads on one kv head (more than one MMA tile of heads in decoding), wide values
     "wide": lambda: config([attention_layer(dim=16, heads=20, kv_heads=1, vdim=80, chunk=70, ff=64),
                             latent_layer(dim=8, heads=18, rot_dim=4, vdim=16, kv_rank=136, ff=0)], vocab=97, width=64),
+    # nothing a multiple of 8: width, key and value widths, rank, feed-forward, vocabulary
+    "odd": lambda: config([attention_layer(dim=10, heads=3, kv_heads=3, vdim=6, chunk=11, ff=50),
+                           latent_layer(dim=10, heads=2, rot_dim=6, vdim=14, kv_rank=22, ff=50),
+                           attention_layer(dim=10, heads=3, kv_heads=3, vdim=6, chunk=40, ff=0)], vocab=101, width=100),
     "attention_only": lambda: config([attention_layer(ff=0, v_mix=False, chunk=9)]),
     "latent_only": lambda: config([latent_layer(ff=0)]),
     "ffn_heavy": lambda: config([attention_layer(heads=2, kv_heads=1, dim=8, vdim=8, chunk=5, ff=160, limit=0.3)]),

@@ -108,7 +108,7 @@ def test_add_norm_with_two_branches(dtype, hidden):
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("name,lengths", [("attention_only", [1, 2, 9, 10, 40]), ("latent_only", [1, 3, 70]),
                                           ("ffn_heavy", [1, 12]), ("mixed", [1, 2, 37, 38, 65, 150]),
-                                          ("even", [64, 131, 300]), ("wide", [5, 71, 141])])
+                                          ("even", [64, 131, 300]), ("wide", [5, 71, 141]), ("odd", [1, 12, 90])])
 def test_each_request_alone_and_whole(name, lengths, dtype):
     eng, cfg, t = engine(name, dtype)
     for k, n in enumerate(lengths):
@@ -117,7 +117,7 @@ def test_each_request_alone_and_whole(name, lengths, dtype):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("name,n,tail", [("mixed", 120, 60), ("wide", 100, 40), ("even", 160, 40)])
+@pytest.mark.parametrize("name,n,tail", [("mixed", 120, 60), ("wide", 100, 40), ("even", 160, 40), ("odd", 70, 30)])
 def test_prefill_against_token_by_token(name, n, tail, dtype):
     eng, cfg, t = engine(name, dtype)
     ids = ids_for(cfg, n, seed=5)
@@ -460,3 +460,22 @@ def test_the_tile_height_the_engine_plans_with_is_the_kernels_own():
     from x0ne_engine_b200.csrc import ops
     assert ops.attention_prefill_tile_rows() == ops.PREFILL_TILE_ROWS
     assert int(ops._lib("flex").x0ne_attention_flex_tile_rows()) == ops.PREFILL_TILE_ROWS
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("pass_rows", [64, 100])
+def test_a_step_larger_than_one_pass(pass_rows, dtype):
+    """A step of more rows than the engine's pass is cut wherever the pass ends, also inside a prompt: the
+    later rows run from the cache the earlier pass left, and the blended values' source is that pass's own."""
+    eng, cfg, t = engine("mixed", dtype, max_step_tokens=pass_rows)
+    base, _, _ = engine("mixed", dtype)
+    prompts = [ids_for(cfg, n, seed=40 + n) for n in (150, 31, 97)]
+    slots = [eng.new_sequence() for _ in prompts]
+    got = eng.step(slots, prompts, [list(range(len(p))) for p in prompts]).cpu().numpy()
+    for s in slots:
+        eng.free_sequence(s)
+    at = 0
+    for p in prompts:
+        same_cut(dtype, got[at:at + len(p)], whole(base, p), f"passes of {pass_rows}")
+        at += len(p)
+    check(dtype, got[:150], H.plain_logits(cfg, t, prompts[0]), "first request")
