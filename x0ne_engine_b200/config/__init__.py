@@ -5,9 +5,12 @@ from .registry import (architectures, config_from_dict, config_from_folder, dete
 from .qwen3 import ARCHITECTURE as _QWEN3, MODEL_TYPE as _QWEN3_TYPE, Qwen3Config
 from .rovurax import ARCHITECTURE as _ROVURAX, MODEL_TYPE as _ROVURAX_TYPE, RovuraxConfig
 
+from .tenetar import ARCHITECTURE as _TENETAR, MODEL_TYPE as _TENETAR_TYPE, TenetarConfig
+
 register_architecture(_QWEN3, _QWEN3_TYPE, Qwen3Config)
+register_architecture(_TENETAR, _TENETAR_TYPE, TenetarConfig)
 register_architecture(_ROVURAX, _ROVURAX_TYPE, RovuraxConfig)
 
-__all__ = ["ConfigError", "LayerSpec", "ModelSpec", "PartSpec", "RunEntry", "Qwen3Config", "RovuraxConfig",
+__all__ = ["ConfigError", "LayerSpec", "ModelSpec", "PartSpec", "RunEntry", "Qwen3Config", "RovuraxConfig", "TenetarConfig",
            "architectures", "config_from_dict", "config_from_folder", "detect",
            "register_architecture", "spec_from_folder", "unregister_architecture"]

@@ -1,8 +1,8 @@
 // Attention over the paged cache in bfloat16 for the shapes and rules the fixed-shape kernels do
 // not take: keys and values of different widths (any width: rows are padded with zeros to a
 // multiple of 16 in shared memory), values that are the leading part of the key rows (a latent
-// cache read by every head), a chunked mask, a sliding window, a per-head sink in the softmax
-// denominator and a per-(row, head) sigmoid gate on the output.
+// cache read by every head), a chunked mask, a sliding window, first keys that stay visible whatever
+// the window, a per-head sink in the softmax denominator and a per-(row, head) sigmoid gate on the output.
 //
 // Both kernels are flash attention on `mma.sync` m16n8k16 with float32 accumulation.  Scores,
 // maxima, sums and weights are float32; for the product with the values a weight p is split into
@@ -236,6 +236,9 @@ flex_prefill_kernel(const bf16* __restrict__ q, bf16* __restrict__ out, PagedCac
     const int64_t k_head = (int64_t)kh * cache.page_size * sh.dk;
     const int64_t v_head = (int64_t)cache.kv_heads * cache.page_size * sh.dk + (int64_t)kh * cache.page_size * sh.vd;
     const int pg_first = key_lo / FX_PAGE, pg_last = key_hi / FX_PAGE;
+    // pages of kept first keys that lie wholly before the first page of the window come first in the walk
+    const int n_kept = min((ex.keep_first + FX_PAGE - 1) / FX_PAGE, pg_first);
+    const int n_walk = n_kept + pg_last - pg_first + 1;
     auto issue = [&](int pg, int stage) -> bool {       // copies page pg into a stage; false if the sequence has no such page
         const int page = fx_page(cache, slot, pg);
         const bf16* pb = page >= 0 ? (const bf16*)cache.base + (int64_t)page * cache.page_stride : nullptr;
@@ -246,29 +249,30 @@ flex_prefill_kernel(const bf16* __restrict__ q, bf16* __restrict__ out, PagedCac
         fx_cp_commit();
         return pb != nullptr;
     };
-    bool have = issue(pg_first, 0);
-    for (int pg = pg_first; pg <= pg_last; ++pg) {
+    bool have = issue(n_kept > 0 ? 0 : pg_first, 0);
+    for (int it = 0; it < n_walk; ++it) {
+        const int pg = it < n_kept ? it : pg_first + it - n_kept;
         const int j0 = pg * FX_PAGE;
-        const int stage = (pg - pg_first) & 1;
+        const int stage = it & 1;
         const bf16* ks = ks0 + stage * stage_elems;
         const bf16* vs = ex.v_from_k > 0 ? ks : ks + FX_PAGE * sh.ks;
         const bool here = have;
-        if (pg < pg_last) {
-            have = issue(pg + 1, stage ^ 1);       // (the stage was last read two pages ago; the barrier at the end of that page covers it)
+        if (it + 1 < n_walk) {
+            have = issue(it + 1 < n_kept ? it + 1 : pg_first + it + 1 - n_kept, stage ^ 1);       // (the stage was last read two pages ago; the barrier at the end of that page covers it)
             fx_cp_wait<1>();
         } else {
             fx_cp_wait<0>();
         }
         __syncthreads();          // this page's tile (and, the first time, the queries) is complete for every warp
         const bool skip = !here;
-        if (warp * 16 >= n_rows || j0 > warp_last || j0 + FX_PAGE <= warp_first_key || skip) {   // nothing of this page for this warp
+        if (warp * 16 >= n_rows || j0 > warp_last || (j0 + FX_PAGE <= warp_first_key && j0 >= ex.keep_first) || skip) {   // nothing of this page for this warp
             __syncthreads();
             continue;
         }
         float s[8][4];
         fx_scores<8>(s, qs + warp * 16 * sh.ks, ks, sh.ks, sh.dkp, 0, lane);
         float mx_a = -INFINITY, mx_b = -INFINITY;
-        if (warp_all_rows && j0 + FX_PAGE - 1 <= warp_first_pos && j0 >= warp_last_key) {
+        if (warp_all_rows && j0 + FX_PAGE - 1 <= warp_first_pos && (j0 >= warp_last_key || j0 + FX_PAGE <= ex.keep_first)) {
             // every key of the page is seen by every row of this warp: no comparisons
 #pragma unroll
             for (int n = 0; n < 8; ++n) {
@@ -283,8 +287,8 @@ flex_prefill_kernel(const bf16* __restrict__ q, bf16* __restrict__ out, PagedCac
 #pragma unroll
                 for (int e = 0; e < 2; ++e) {
                     const int j = j0 + 8 * n + 2 * t + e;
-                    s[n][e] = (ok_a && j <= pos_a && j >= lo_a) ? s[n][e] * sc2 : -INFINITY;
-                    s[n][2 + e] = (ok_b && j <= pos_b && j >= lo_b) ? s[n][2 + e] * sc2 : -INFINITY;
+                    s[n][e] = (ok_a && j <= pos_a && (j >= lo_a || j < ex.keep_first)) ? s[n][e] * sc2 : -INFINITY;
+                    s[n][2 + e] = (ok_b && j <= pos_b && (j >= lo_b || j < ex.keep_first)) ? s[n][2 + e] * sc2 : -INFINITY;
                     mx_a = fmaxf(mx_a, s[n][e]);
                     mx_b = fmaxf(mx_b, s[n][2 + e]);
                 }
@@ -380,8 +384,12 @@ flex_decode_kernel(const bf16* __restrict__ q, bf16* __restrict__ out, PagedCach
     const float sc2 = scale * FX_LOG2E;
     const int key_lo = fx_first_key(pos, window, ex.chunk);
     const int pg_lo = key_lo / FX_PAGE, pg_hi = slot >= 0 ? pos / FX_PAGE : pg_lo - 1;
-    const int per = (pg_hi - pg_lo + 1 + splits - 1) / splits;
-    const int pg_a = pg_lo + split * per, pg_b = min(pg_hi, pg_a + per - 1);
+    // the walk: pages of kept first keys that lie wholly before the window's first page, then the window's pages
+    const int n_kept = slot >= 0 ? min((ex.keep_first + FX_PAGE - 1) / FX_PAGE, pg_lo) : 0;
+    const int n_walk = n_kept + pg_hi - pg_lo + 1;
+    const int per = (n_walk + splits - 1) / splits;
+    const int it_a = split * per, it_b = min(n_walk - 1, it_a + per - 1);
+    auto page_at = [&](int it) -> int { return it < n_kept ? it : pg_lo + it - n_kept; };
     float m_a = -INFINITY, m_b = -INFINITY, l_a = 0.f, l_b = 0.f;
     float o[DVT][4];
 #pragma unroll
@@ -402,23 +410,23 @@ flex_decode_kernel(const bf16* __restrict__ q, bf16* __restrict__ out, PagedCach
     // slot, also an empty one, so that "all but the newest FX_DECODE_STAGES - 1 groups" is always this page's
     unsigned have = 0;                       // bit s: the page in stage s exists
     for (int i = 0; i < FX_DECODE_STAGES - 1; ++i) {
-        if (pg_a + i <= pg_b) have |= issue(pg_a + i, i) ? 1u << i : 0u;
+        if (it_a + i <= it_b) have |= issue(page_at(it_a + i), i) ? 1u << i : 0u;
         else fx_cp_commit();
     }
-    for (int pg = pg_a; pg <= pg_b; ++pg) {
-        const int j0 = pg * FX_PAGE;
-        const int stage = (pg - pg_a) % FX_DECODE_STAGES;
+    for (int it = it_a; it <= it_b; ++it) {
+        const int j0 = page_at(it) * FX_PAGE;
+        const int stage = (it - it_a) % FX_DECODE_STAGES;
         const bf16* ks = ks0 + stage * stage_elems;
         const bf16* vs = ex.v_from_k > 0 ? ks : ks + FX_PAGE * sh.ks;
-        const int ahead = pg + FX_DECODE_STAGES - 1, ahead_stage = (ahead - pg_a) % FX_DECODE_STAGES;
+        const int ahead = it + FX_DECODE_STAGES - 1, ahead_stage = (ahead - it_a) % FX_DECODE_STAGES;
         have &= ~(1u << ahead_stage);        // (that stage was read one page ago; the barrier at that page's end covers it)
-        if (ahead <= pg_b) have |= issue(ahead, ahead_stage) ? 1u << ahead_stage : 0u;
+        if (ahead <= it_b) have |= issue(page_at(ahead), ahead_stage) ? 1u << ahead_stage : 0u;
         else fx_cp_commit();
         fx_cp_wait<FX_DECODE_STAGES - 1>();
         __syncthreads();
         const bool here = (have >> stage) & 1u;
         const int jw = j0 + 16 * warp;           // this warp's 16 keys of the page
-        if (!here || jw > pos || jw + 16 <= key_lo) {
+        if (!here || jw > pos || (jw + 16 <= key_lo && jw >= ex.keep_first)) {
             __syncthreads();
             continue;
         }
@@ -429,7 +437,7 @@ flex_decode_kernel(const bf16* __restrict__ q, bf16* __restrict__ out, PagedCach
 #pragma unroll
             for (int e = 0; e < 2; ++e) {
                 const int j = jw + 8 * n + 2 * t + e;
-                const bool vis = j <= pos && j >= key_lo;
+                const bool vis = j <= pos && (j >= key_lo || j < ex.keep_first);
                 s[n][e] = vis ? s[n][e] * sc2 : -INFINITY;
                 s[n][2 + e] = vis ? s[n][2 + e] * sc2 : -INFINITY;
             }
@@ -638,7 +646,7 @@ X0NE_API int x0ne_attention_flex_prefill(const void* q, void* out, PagedCache ca
                                          AttnExtra ex, cudaStream_t stream) {
     X0NE_REQUIRE(n_tiles >= 0 && q_heads > 0 && cache.kv_heads > 0 && q_heads % cache.kv_heads == 0 && q_heads <= 65535,
                  "attention_flex: %d q heads over %d kv heads", q_heads, cache.kv_heads);
-    X0NE_REQUIRE(window >= 0 && ex.chunk >= 0, "attention_flex: negative window or chunk");
+    X0NE_REQUIRE(window >= 0 && ex.chunk >= 0 && ex.keep_first >= 0, "attention_flex: negative window, chunk or count of kept keys");
     FxShape sh;
     if (int e = fx_shape(cache, ex, &sh)) return e;
     if (n_tiles == 0) return 0;
@@ -675,7 +683,7 @@ X0NE_API int x0ne_attention_flex_decode(const void* q, void* out, PagedCache cac
                                         int splits, void* scratch, int64_t scratch_bytes, cudaStream_t stream) {
     X0NE_REQUIRE(n_rows >= 0 && q_heads > 0 && cache.kv_heads > 0 && q_heads % cache.kv_heads == 0,
                  "attention_flex: %d q heads over %d kv heads", q_heads, cache.kv_heads);
-    X0NE_REQUIRE(window >= 0 && ex.chunk >= 0 && splits >= 1 && splits <= FX_MAX_SPLITS, "attention_flex: window, chunk or splits (1 to %d) out of range", FX_MAX_SPLITS);
+    X0NE_REQUIRE(window >= 0 && ex.chunk >= 0 && ex.keep_first >= 0 && splits >= 1 && splits <= FX_MAX_SPLITS, "attention_flex: window, chunk or splits (1 to %d) out of range", FX_MAX_SPLITS);
     FxShape sh;
     if (int e = fx_shape(cache, ex, &sh)) return e;
     if (n_rows == 0) return 0;

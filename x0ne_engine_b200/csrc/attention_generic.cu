@@ -18,7 +18,8 @@
 //
 // Beyond that (`AttnExtra`): a chunked mask (the query sees its own chunk of positions only), a
 // value width other than the keys', values read out of the key rows, a per-head sink in the
-// denominator, and a per-(row, head) sigmoid gate on the output.  With none of them asked for the
+// denominator, a per-(row, head) sigmoid gate on the output, and first keys that stay visible
+// whatever the window (they are taken first, in tiles of 32 from key 0, then the window's).  With none of them asked for the
 // operations and their order are the ones above.
 
 #define ATT_MAX_I 16  // value width <= 32 * ATT_MAX_I
@@ -51,11 +52,15 @@ __global__ void attention_rows_kernel(const T* __restrict__ q, T* __restrict__ o
 #pragma unroll
     for (int i = 0; i < ATT_MAX_I; ++i) acc[i] = 0.f;
 
-    for (int j0 = j_lo; j0 <= pos; j0 += 32) {
+    // the kept first keys that lie before the window (tiles of 32 from key 0), then the window's keys
+    const int kept = min(ex.keep_first, j_lo);
+    for (int seg = kept > 0 ? 0 : 1; seg < 2; ++seg) {
+    const int j_end = seg == 0 ? kept - 1 : pos;
+    for (int j0 = seg == 0 ? 0 : j_lo; j0 <= j_end; j0 += 32) {
         const int j = j0 + lane;
         int64_t off = -1;
         float s = -INFINITY;
-        if (j <= pos) {
+        if (j <= j_end) {
             off = cache_row_offset(cache, slot, j, kh, 0);
             if (off >= 0) {
                 const T* kr = base + off;
@@ -71,7 +76,7 @@ __global__ void attention_rows_kernel(const T* __restrict__ q, T* __restrict__ o
         l = l * alpha + warp_sum(p);
 #pragma unroll
         for (int i = 0; i < ATT_MAX_I; ++i) acc[i] *= alpha;
-        const int nt = min(32, pos - j0 + 1);
+        const int nt = min(32, j_end - j0 + 1);
         for (int t = 0; t < nt; ++t) {
             const float pt = __shfl_sync(0xffffffffu, p, t);
             const long long ot = __shfl_sync(0xffffffffu, (long long)off, t);
@@ -86,6 +91,7 @@ __global__ void attention_rows_kernel(const T* __restrict__ q, T* __restrict__ o
             }
         }
         m = m_new;
+    }
     }
     if (ex.sink != nullptr && slot >= 0) {
         const float sk = ex.sink[head];
@@ -113,7 +119,7 @@ X0NE_API int x0ne_attention_rows_ex(const void* q, void* out, int dt, PagedCache
     const int vd = ex.v_from_k > 0 ? ex.v_from_k : cache_v_dim(cache);
     X0NE_REQUIRE(cache.head_dim > 0 && cache.head_dim <= 2048 && vd > 0 && vd <= 32 * ATT_MAX_I && ex.v_from_k <= cache.head_dim,
                  "attention: keys of %d and values of %d are beyond the plain kernel's limits of 2048 and %d", cache.head_dim, vd, 32 * ATT_MAX_I);
-    X0NE_REQUIRE(window >= 0 && ex.chunk >= 0, "attention: negative window or chunk");
+    X0NE_REQUIRE(window >= 0 && ex.chunk >= 0 && ex.keep_first >= 0, "attention: negative window, chunk or count of kept keys");
     if (n_rows == 0) return 0;
     const int warps = 4;
     const int64_t items = (int64_t)n_rows * q_heads;

@@ -204,6 +204,7 @@ struct AttnExtra {
     const void* gate;     // per (row, q head) in the activation type, or null: the head's output is multiplied by sigmoid(gate)
     int64_t gate_ld;      // values between the gates of consecutive rows
     int64_t q_ld;         // values between consecutive query rows (0: q heads x head_dim)
+    int32_t keep_first;   // > 0: besides its window or chunk a query sees the keys at positions below this (at their true positions)
 };
 
 // Element offset of (slot, pos, kv head, which = 0 for K / 1 for V); -1 if there is no page, or if

@@ -231,6 +231,127 @@ X0NE_API int x0ne_add_rmsnorm(float* resid, const void* delta, const float* w, v
 }
 
 // ----------------------------------------------------------------------------------------
+// Residual add of a delta that is normed first, then RMSNorm (a layer with a norm after each
+// sublayer as well as before it):
+//   d = f32(delta) * rsqrt(mean(delta^2) + eps_d) * w_d     (float32, never rounded)
+//   r = resid + d (stored back);  out = T(r * rsqrt(mean(r^2) + eps) * w)
+// Same rows / block conventions as above; both sums of squares are fixed-order block sums.
+// ----------------------------------------------------------------------------------------
+template <typename T>
+__global__ void add_normed_rmsnorm_any_kernel(float* __restrict__ resid, const T* __restrict__ delta, const float* __restrict__ w_d,
+                                              float eps_d, const float* __restrict__ w, T* __restrict__ out,
+                                              const int32_t* __restrict__ rows, int hidden, float eps, int keep) {
+    extern __shared__ float parked[];
+    __shared__ float partial[32];
+    pdl_prologue();
+    const int64_t src = rows ? rows[blockIdx.x] : blockIdx.x;
+    float* r = resid + src * hidden;
+    const T* d = delta + src * hidden;
+    float dd = 0.f;
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+        const float v = to_f32(d[i]);
+        dd = fmaf(v, v, dd);
+    }
+    const float scale_d = 1.0f / sqrtf(block_reduce(dd, partial, OpSum(), 0.f) / (float)hidden + eps_d);
+    float sum_sq = 0.f;
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+        const float v = r[i] + to_f32(d[i]) * scale_d * w_d[i];
+        r[i] = v;
+        if (i < keep) parked[i] = v;
+        sum_sq = fmaf(v, v, sum_sq);
+    }
+    const float scale = 1.0f / sqrtf(block_reduce(sum_sq, partial, OpSum(), 0.f) / (float)hidden + eps);
+    T* o = out + (int64_t)blockIdx.x * hidden;
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+        const float v = i < keep ? parked[i] : r[i];
+        o[i] = from_f32<T>(v * scale * w[i]);
+    }
+}
+
+// hidden % 8 == 0 and hidden <= 8 * 1024 * 2: 16-byte accesses, the row and the delta stay in registers.
+template <typename T, int ITS>
+__global__ void __launch_bounds__(1024) add_normed_rmsnorm_vec_kernel(float* __restrict__ resid, const T* __restrict__ delta, const float* __restrict__ w_d,
+                                              float eps_d, const float* __restrict__ w, T* __restrict__ out,
+                                              const int32_t* __restrict__ rows, int hidden, float eps) {
+    __shared__ float sh[32];
+    pdl_launch_dependents();
+    const int64_t src = rows ? rows[blockIdx.x] : blockIdx.x;
+    pdl_wait();
+    float* r = resid + src * hidden;
+    const T* d = delta + src * hidden;
+    T* o = out + (int64_t)blockIdx.x * hidden;
+    float dv[ITS][8], v[ITS][8];
+    float dd = 0.f;
+#pragma unroll
+    for (int it = 0; it < ITS; ++it) {
+        const int i = (it * blockDim.x + threadIdx.x) * 8;
+        if (i < hidden) {
+            load8(d + i, dv[it]);
+            load8(r + i, v[it]);
+#pragma unroll
+            for (int k = 0; k < 8; ++k) dd += dv[it][k] * dv[it][k];
+        }
+    }
+    const float scale_d = 1.0f / sqrtf(block_sum(dd, sh) / (float)hidden + eps_d);
+    float ss = 0.f;
+#pragma unroll
+    for (int it = 0; it < ITS; ++it) {
+        const int i = (it * blockDim.x + threadIdx.x) * 8;
+        if (i < hidden) {
+            float wd[8];
+            load8(w_d + i, wd);
+#pragma unroll
+            for (int k = 0; k < 8; ++k) {
+                v[it][k] = v[it][k] + dv[it][k] * scale_d * wd[k];
+                ss += v[it][k] * v[it][k];
+            }
+            store8(r + i, v[it]);
+        }
+    }
+    const float scale = 1.0f / sqrtf(block_sum(ss, sh) / (float)hidden + eps);
+#pragma unroll
+    for (int it = 0; it < ITS; ++it) {
+        const int i = (it * blockDim.x + threadIdx.x) * 8;
+        if (i < hidden) {
+            float wv[8], ov[8];
+            load8(w + i, wv);
+#pragma unroll
+            for (int k = 0; k < 8; ++k) ov[k] = v[it][k] * scale * wv[k];
+            store8(o + i, ov);
+        }
+    }
+}
+
+X0NE_API int x0ne_add_normed_rmsnorm(float* resid, const void* delta, const float* w_d, float eps_d, const float* w, void* out,
+                                     int dt, const int32_t* rows, int n_rows, int hidden, float eps, cudaStream_t stream) {
+    X0NE_REQUIRE(n_rows >= 0 && hidden > 0 && delta != nullptr && w_d != nullptr, "add_normed_rmsnorm: rows %d hidden %d", n_rows, hidden);
+    X0NE_REQUIRE(dt == X0NE_F32 || dt == X0NE_BF16, "add_normed_rmsnorm: unknown dtype tag %d", dt);
+    if (n_rows == 0) return 0;
+    if (hidden % 8 == 0 && hidden <= 8 * 1024 * 2 &&
+        ((((uintptr_t)resid | (uintptr_t)delta | (uintptr_t)w_d | (uintptr_t)w | (uintptr_t)out) & 15) == 0)) {
+        int threads = (hidden / 8 + 31) / 32 * 32;
+        if (threads > 1024) threads = 1024;
+        if (hidden / 8 > 512 && hidden / 8 <= 1024) threads = 512;
+        const int sweeps = (hidden / 8 + threads - 1) / threads;
+#define X0NE_ANR(T, ITS) x0ne_launch(add_normed_rmsnorm_vec_kernel<T, ITS>, dim3(n_rows), dim3(threads), 0, stream, resid, (const T*)delta, w_d, eps_d, w, (T*)out, rows, hidden, eps)
+        if (dt == X0NE_F32) {
+            if (sweeps <= 1) X0NE_ANR(float, 1); else X0NE_ANR(float, 2);
+        } else {
+            if (sweeps <= 1) X0NE_ANR(bf16, 1); else X0NE_ANR(bf16, 2);
+        }
+#undef X0NE_ANR
+        X0NE_LAUNCH_CHECK();
+    }
+    const int keep = hidden <= 10240 ? hidden : 0;
+    const size_t smem = (size_t)keep * sizeof(float);
+    if (dt == X0NE_F32)
+        x0ne_launch(add_normed_rmsnorm_any_kernel<float>, dim3(n_rows), dim3(256), smem, stream, resid, (const float*)delta, w_d, eps_d, w, (float*)out, rows, hidden, eps, keep);
+    else
+        x0ne_launch(add_normed_rmsnorm_any_kernel<bf16>, dim3(n_rows), dim3(256), smem, stream, resid, (const bf16*)delta, w_d, eps_d, w, (bf16*)out, rows, hidden, eps, keep);
+    X0NE_LAUNCH_CHECK();
+}
+
+// ----------------------------------------------------------------------------------------
 // Per-head RMSNorm of q and k (optional), rotate-half RoPE, and the K/V write into the
 // paged cache (x0ne-core/kernels/cuda/rope.cu:7-47).  One warp per (row, head); the row's sines and
 // cosines come from a table made at start-up (or are computed by the warp); heads
@@ -599,7 +720,7 @@ X0NE_API int x0ne_swiglu(const void* gate_up, void* out, int dt, int n_rows, int
 // ----------------------------------------------------------------------------------------
 template <typename T>
 __global__ void embedding_kernel(const T* __restrict__ table, const int32_t* __restrict__ tokens,
-                                 float* __restrict__ resid, int hidden, int vocab) {
+                                 float* __restrict__ resid, int hidden, int vocab, float scale) {
     pdl_prologue();
     const int row = blockIdx.x;
     const int t = tokens[row];
@@ -609,14 +730,14 @@ __global__ void embedding_kernel(const T* __restrict__ table, const int32_t* __r
         return;
     }
     const T* src = table + (int64_t)t * hidden;
-    for (int i = threadIdx.x; i < hidden; i += blockDim.x) dst[i] = to_f32(src[i]);
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x) dst[i] = to_f32(src[i]) * scale;
 }
 
 // The same with 16-byte accesses (hidden % 8 == 0, aligned rows): all of a row's loads are in flight
 // at once, where the loop above waits for memory once per 256 values (9.5 us for 8 rows of 4,096).
 template <typename T>
 __global__ void embedding_vec_kernel(const T* __restrict__ table, const int32_t* __restrict__ tokens,
-                                     float* __restrict__ resid, int hidden, int vocab) {
+                                     float* __restrict__ resid, int hidden, int vocab, float scale) {
     pdl_prologue();
     const int row = blockIdx.x;
     const int t = tokens[row];
@@ -634,33 +755,32 @@ __global__ void embedding_vec_kernel(const T* __restrict__ table, const int32_t*
         for (int u = 0; u < 4; ++u) {
             const int i = i0 + u * blockDim.x * 8;
             if (i < hidden) {
-                if (none) {
 #pragma unroll
-                    for (int k = 0; k < 8; ++k) v[u][k] = 0.f;
-                }
+                for (int k = 0; k < 8; ++k) v[u][k] = none ? 0.f : v[u][k] * scale;
                 store8(dst + i, v[u]);
             }
         }
     }
 }
 
+// `scale` multiplies every value in float32 (1: the row itself, the same bits).
 X0NE_API int x0ne_embedding(const void* table, int dt, const int32_t* tokens, float* resid, int n_rows,
-                            int hidden, int vocab, cudaStream_t stream) {
+                            int hidden, int vocab, float scale, cudaStream_t stream) {
     X0NE_REQUIRE(n_rows >= 0 && hidden > 0 && vocab > 0, "embedding: rows %d hidden %d vocab %d", n_rows, hidden, vocab);
     if (n_rows == 0) return 0;
     const int block = hidden >= 1024 ? 256 : 128;
     if (hidden % 8 == 0 && (((uintptr_t)table | (uintptr_t)resid) & 15) == 0 && (dt == X0NE_F32 || dt == X0NE_BF16)) {
         const int threads = hidden / 8 >= 256 ? 256 : (hidden / 8 + 31) / 32 * 32;
         if (dt == X0NE_F32)
-            x0ne_launch(embedding_vec_kernel<float>, dim3(n_rows), dim3(threads), 0, stream, (const float*)table, tokens, resid, hidden, vocab);
+            x0ne_launch(embedding_vec_kernel<float>, dim3(n_rows), dim3(threads), 0, stream, (const float*)table, tokens, resid, hidden, vocab, scale);
         else
-            x0ne_launch(embedding_vec_kernel<bf16>, dim3(n_rows), dim3(threads), 0, stream, (const bf16*)table, tokens, resid, hidden, vocab);
+            x0ne_launch(embedding_vec_kernel<bf16>, dim3(n_rows), dim3(threads), 0, stream, (const bf16*)table, tokens, resid, hidden, vocab, scale);
         X0NE_LAUNCH_CHECK();
     }
     if (dt == X0NE_F32)
-        x0ne_launch(embedding_kernel<float>, dim3(n_rows), dim3(block), 0, stream, (const float*)table, tokens, resid, hidden, vocab);
+        x0ne_launch(embedding_kernel<float>, dim3(n_rows), dim3(block), 0, stream, (const float*)table, tokens, resid, hidden, vocab, scale);
     else if (dt == X0NE_BF16)
-        x0ne_launch(embedding_kernel<bf16>, dim3(n_rows), dim3(block), 0, stream, (const bf16*)table, tokens, resid, hidden, vocab);
+        x0ne_launch(embedding_kernel<bf16>, dim3(n_rows), dim3(block), 0, stream, (const bf16*)table, tokens, resid, hidden, vocab, scale);
     else
         X0NE_REQUIRE(false, "embedding: unknown dtype tag %d", dt);
     X0NE_LAUNCH_CHECK();

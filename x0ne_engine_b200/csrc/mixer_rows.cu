@@ -293,3 +293,153 @@ X0NE_API int x0ne_latent_prepare(const void* src, int dt, int ld, int dkv_col, c
         X0NE_REQUIRE(false, "latent_prepare: unknown dtype tag %d", dt);
     X0NE_LAUNCH_CHECK();
 }
+
+// ----------------------------------------------------------------------------------------
+// Attention rows whose queries and keys are normed over the WHOLE projection (all heads at once,
+// one weight per projected value) before they are split into heads and rotated:
+//   q_n = q * rsqrt(mean(q^2 over q_heads x dim) + eps) * w_q      (k alike, over kv_heads x dim)
+//   rotation of the first `rot` values of every head, value i with value i + rot/2, by pos * freq[i]
+//   q_n -> q_out; k_n -> cache keys; v -> cache values (as they are).
+// `src` rows of `ld` values hold the queries at column 0, the keys at k_col and the values at v_col.
+// write_kv == 0: a layer that reads another layer's keys and values; only the queries are made.
+// Norms, angles and the rotation are float32; one rounding at the store.  One block per row.
+// `table` (float32 [positions][rot]: rot/2 cosines then rot/2 sines) replaces sincosf for the
+// positions it covers.
+// ----------------------------------------------------------------------------------------
+template <typename T>
+__global__ void whole_norm_rope_kv_write_kernel(const T* __restrict__ src, int ld, int k_col, int v_col,
+                                                const float* __restrict__ norm_q, const float* __restrict__ norm_k, float eps,
+                                                const float* __restrict__ freq, int rot, const float* __restrict__ table,
+                                                int table_positions, T* __restrict__ q_out, int q_heads, PagedCache cache,
+                                                const int32_t* __restrict__ row_slot, const int32_t* __restrict__ row_pos,
+                                                int write_kv) {
+    extern __shared__ float cs[];          // rot/2 cosines, rot/2 sines
+    __shared__ float partial[32];
+    pdl_launch_dependents();
+    const int row = blockIdx.x;
+    const int slot = row_slot[row], pos = row_pos[row];
+    const int half = rot / 2;
+    for (int i = threadIdx.x; i < half; i += blockDim.x) {
+        if (pos >= 0 && pos < table_positions) {
+            cs[i] = table[(int64_t)pos * rot + i];
+            cs[half + i] = table[(int64_t)pos * rot + half + i];
+        } else {
+            float sn, c;
+            sincosf((float)pos * freq[i], &sn, &c);
+            cs[i] = c;
+            cs[half + i] = sn;
+        }
+    }
+    pdl_wait();
+    const int D = cache.head_dim, G = cache.kv_heads, vd = cache_v_dim(cache);
+    const int qn = q_heads * D, kn = G * D;
+    const T* s = src + (int64_t)row * ld;
+    float sq = 0.f, sk = 0.f;
+    for (int i = threadIdx.x; i < qn; i += blockDim.x) {
+        const float v = to_f32(s[i]);
+        sq = fmaf(v, v, sq);
+    }
+    if (write_kv)
+        for (int i = threadIdx.x; i < kn; i += blockDim.x) {
+            const float v = to_f32(s[k_col + i]);
+            sk = fmaf(v, v, sk);
+        }
+    const float scale_q = 1.0f / sqrtf(block_reduce(sq, partial, OpSum(), 0.f) / (float)qn + eps);   // (syncs: cs is complete)
+    T* qo = q_out + (int64_t)row * qn;
+    for (int i = threadIdx.x; i < qn; i += blockDim.x) {
+        const int d = i % D;
+        float a = to_f32(s[i]) * scale_q * norm_q[i];
+        if (d < rot) {
+            const int j = d < half ? d : d - half;
+            const int ip = d < half ? i + half : i - half;
+            const float b = to_f32(s[ip]) * scale_q * norm_q[ip];
+            a = d < half ? a * cs[j] - b * cs[half + j] : a * cs[j] + b * cs[half + j];
+        }
+        qo[i] = from_f32<T>(a);
+    }
+    if (!write_kv) return;
+    const float scale_k = 1.0f / sqrtf(block_reduce(sk, partial, OpSum(), 0.f) / (float)kn + eps);
+    const int64_t k0 = cache_row_offset(cache, slot, pos, 0, 0);
+    if (k0 < 0) return;
+    T* base = (T*)cache.base;
+    const int64_t head_k = (int64_t)cache.page_size * D, head_v = (int64_t)cache.page_size * vd;
+    for (int i = threadIdx.x; i < kn; i += blockDim.x) {
+        const int d = i % D;
+        float a = to_f32(s[k_col + i]) * scale_k * norm_k[i];
+        if (d < rot) {
+            const int j = d < half ? d : d - half;
+            const int ip = d < half ? i + half : i - half;
+            const float b = to_f32(s[k_col + ip]) * scale_k * norm_k[ip];
+            a = d < half ? a * cs[j] - b * cs[half + j] : a * cs[j] + b * cs[half + j];
+        }
+        base[k0 + (i / D) * head_k + d] = from_f32<T>(a);
+    }
+    const int64_t v0 = cache_row_offset(cache, slot, pos, 0, 1);
+    for (int i = threadIdx.x; i < G * vd; i += blockDim.x) base[v0 + (i / vd) * head_v + (i % vd)] = s[v_col + i];
+}
+
+X0NE_API int x0ne_whole_norm_rope_kv_write(const void* src, int dt, int ld, int k_col, int v_col, const float* norm_q,
+                                           const float* norm_k, float eps, const float* freq, int rot, const float* table,
+                                           int table_positions, void* q_out, int q_heads, PagedCache cache,
+                                           const int32_t* row_slot, const int32_t* row_pos, int n_rows, int write_kv,
+                                           cudaStream_t stream) {
+    X0NE_REQUIRE(n_rows >= 0 && q_heads > 0 && ld >= q_heads * cache.head_dim && rot >= 0 && rot % 2 == 0 && rot <= cache.head_dim,
+                 "whole_norm_rope: rows %d heads %d ld %d rot %d head_dim %d", n_rows, q_heads, ld, rot, cache.head_dim);
+    X0NE_REQUIRE(norm_q != nullptr && (rot == 0 || freq != nullptr), "whole_norm_rope: no norm weight or no frequencies");
+    if (write_kv) {
+        X0NE_REQUIRE(cache.v_dim >= 0 && norm_k != nullptr, "whole_norm_rope: the cache keeps no values, or no key norm weight");
+        X0NE_REQUIRE(k_col >= q_heads * cache.head_dim && k_col + cache.kv_heads * cache.head_dim <= ld && v_col >= 0 &&
+                     v_col + cache.kv_heads * cache_v_dim(cache) <= ld, "whole_norm_rope: keys or values lie outside the source rows");
+    }
+    if (n_rows == 0) return 0;
+    const size_t smem = (size_t)(rot > 0 ? rot : 2) * sizeof(float);
+    if (dt == X0NE_F32)
+        x0ne_launch(whole_norm_rope_kv_write_kernel<float>, dim3(n_rows), dim3(256), smem, stream, (const float*)src, ld, k_col, v_col, norm_q, norm_k, eps, freq, rot, table, table_positions, (float*)q_out, q_heads, cache, row_slot, row_pos, write_kv);
+    else if (dt == X0NE_BF16)
+        x0ne_launch(whole_norm_rope_kv_write_kernel<bf16>, dim3(n_rows), dim3(256), smem, stream, (const bf16*)src, ld, k_col, v_col, norm_q, norm_k, eps, freq, rot, table, table_positions, (bf16*)q_out, q_heads, cache, row_slot, row_pos, write_kv);
+    else
+        X0NE_REQUIRE(false, "whole_norm_rope: unknown dtype tag %d", dt);
+    X0NE_LAUNCH_CHECK();
+}
+
+// ----------------------------------------------------------------------------------------
+// Squared ReLU in place or out of place: out = max(x, 0)^2, float32 arithmetic.
+// ----------------------------------------------------------------------------------------
+template <typename T>
+__global__ void relu2_kernel(const T* __restrict__ x, T* __restrict__ out, int64_t total) {
+    pdl_prologue();
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+        const float v = fmaxf(to_f32(x[i]), 0.f);
+        out[i] = from_f32<T>(v * v);
+    }
+}
+template <typename T>
+__global__ void relu2_vec_kernel(const T* __restrict__ x, T* __restrict__ out, int64_t total8) {
+    pdl_prologue();
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total8; i += (int64_t)gridDim.x * blockDim.x) {
+        float v[8];
+        load8f(x + i * 8, v);
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+            v[k] = fmaxf(v[k], 0.f);
+            v[k] *= v[k];
+        }
+        store8f(out + i * 8, v);
+    }
+}
+
+X0NE_API int x0ne_relu2(const void* x, void* out, int dt, int64_t total, cudaStream_t stream) {
+    X0NE_REQUIRE(total >= 0 && (dt == X0NE_F32 || dt == X0NE_BF16), "relu2: %lld values, dtype tag %d", (long long)total, dt);
+    if (total == 0) return 0;
+    if (total % 8 == 0 && ((((uintptr_t)x | (uintptr_t)out) & 31) == 0)) {
+        const int64_t t8 = total / 8;
+        const unsigned grid = (unsigned)((t8 + 255) / 256 < 65535 * 16 ? (t8 + 255) / 256 : 65535 * 16);
+        if (dt == X0NE_F32) x0ne_launch(relu2_vec_kernel<float>, dim3(grid), dim3(256), 0, stream, (const float*)x, (float*)out, t8);
+        else x0ne_launch(relu2_vec_kernel<bf16>, dim3(grid), dim3(256), 0, stream, (const bf16*)x, (bf16*)out, t8);
+        X0NE_LAUNCH_CHECK();
+    }
+    const unsigned grid = (unsigned)((total + 255) / 256 < 65535 * 16 ? (total + 255) / 256 : 65535 * 16);
+    if (dt == X0NE_F32) x0ne_launch(relu2_kernel<float>, dim3(grid), dim3(256), 0, stream, (const float*)x, (float*)out, total);
+    else x0ne_launch(relu2_kernel<bf16>, dim3(grid), dim3(256), 0, stream, (const bf16*)x, (bf16*)out, total);
+    X0NE_LAUNCH_CHECK();
+}

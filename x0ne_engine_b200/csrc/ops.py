@@ -46,15 +46,16 @@ class AttnExtraArg(Structure):
     """Mirror of `struct AttnExtra` in common.cuh: what an attention kernel is asked for beyond causal
     softmax over a window (all zero: nothing)."""
     _fields_ = [("chunk", c_int32), ("v_from_k", c_int32), ("sink", c_void_p), ("gate", c_void_p),
-                ("gate_ld", c_int64), ("q_ld", c_int64)]
+                ("gate_ld", c_int64), ("q_ld", c_int64), ("keep_first", c_int32)]
 
 
 def attn_extra(chunk: int = 0, v_from_k: int = 0, sink: Optional[torch.Tensor] = None, gate: Optional[torch.Tensor] = None,
-               gate_ld: int = 0, q_ld: int = 0) -> AttnExtraArg:
-    """`sink`: float32 per q head.  `gate`: a view whose element (row, head) lies at row * gate_ld + head."""
+               gate_ld: int = 0, q_ld: int = 0, keep_first: int = 0) -> AttnExtraArg:
+    """`sink`: float32 per q head.  `gate`: a view whose element (row, head) lies at row * gate_ld + head.
+    `keep_first`: the keys at positions below it stay visible to every later query, whatever the window or chunk."""
     if sink is not None:
         _need(sink, torch.float32, "sink")
-    return AttnExtraArg(int(chunk or 0), int(v_from_k or 0), _ptr(sink), _ptr(gate), int(gate_ld), int(q_ld))
+    return AttnExtraArg(int(chunk or 0), int(v_from_k or 0), _ptr(sink), _ptr(gate), int(gate_ld), int(q_ld), int(keep_first or 0))
 
 
 class SampleIOArg(Structure):
@@ -73,7 +74,14 @@ _P, _I, _F, _L = c_void_p, c_int, c_float, c_int64
 # numbers itself, which is about a third of the cost of building a c_int or c_void_p per argument
 # and per call (1.4 us against 3.8 us for ten arguments).  Pointers are passed as integers.
 _SIGNATURES = {
-    "x0ne_embedding": [_P, _I, _P, _P, _I, _I, _I, _P],
+    "x0ne_embedding": [_P, _I, _P, _P, _I, _I, _I, _F, _P],
+    "x0ne_add_normed_rmsnorm": [_P, _P, _P, _F, _P, _P, _I, _P, _I, _I, _F, _P],
+    "x0ne_whole_norm_rope_kv_write": [_P, _I, _I, _I, _I, _P, _P, _F, _P, _I, _P, _I, _P, _I, None, _P, _P, _I, _I, _P],
+    "x0ne_relu2": [_P, _P, _I, _L, _P],
+    "x0ne_moe_route": [_P, _I, _P, _I, _I, _I, _I, _I, _P, _P, _P, _I, _P],
+    "x0ne_moe_group": [_P, _I, _I, _P, _P, _P, _I, _P],
+    "x0ne_moe_product": [_I, _P, _L, _P, _I, _I, _I, _P, _P, _I, _I, _P, _P],
+    "x0ne_moe_combine": [_P, _P, _I, _P, _P, _I, _I, _P, _P, _P, _I, _I, _P],
     "x0ne_add_rmsnorm": [_P, _P, _P, _P, _I, _P, _I, _I, _F, _P],
     "x0ne_add2_rmsnorm": [_P, _P, _P, _P, _P, _I, _P, _I, _I, _F, _P],
     "x0ne_glu_clipped": [_P, _P, _I, _I, _I, _F, _F, _F, _P],
@@ -174,8 +182,8 @@ def plan_pass(slots, starts, first_row, tokens, r0: int, r1: int, want_sorted, t
     return tuple(out)
 
 
-def embedding(table: torch.Tensor, tokens: torch.Tensor, resid: torch.Tensor, n_rows: int) -> None:
-    """resid[r] = float32(table[tokens[r]]); an id outside the table gives a zero row."""
+def embedding(table: torch.Tensor, tokens: torch.Tensor, resid: torch.Tensor, n_rows: int, scale: float = 1.0) -> None:
+    """resid[r] = float32(table[tokens[r]]) * scale; an id outside the table gives a zero row."""
     lib = _lib("core")
     _need(tokens, torch.int32, "tokens")
     _need(resid, torch.float32, "residual")
@@ -184,7 +192,7 @@ def embedding(table: torch.Tensor, tokens: torch.Tensor, resid: torch.Tensor, n_
     if resid.shape[-1] != hidden or resid.numel() < n_rows * hidden or tokens.numel() < n_rows:
         raise KernelError("embedding: buffers are smaller than the rows asked for")
     _check(lib, lib.x0ne_embedding(_ptr(table), dtype_tag(table.dtype), _ptr(tokens), _ptr(resid),
-                                   n_rows, hidden, vocab, _stream()), "embedding")
+                                   n_rows, hidden, vocab, float(scale), _stream()), "embedding")
 
 
 def add_rmsnorm(resid: torch.Tensor, delta, weight: torch.Tensor, out: torch.Tensor,
@@ -225,6 +233,169 @@ def add_rmsnorm(resid: torch.Tensor, delta, weight: torch.Tensor, out: torch.Ten
         return
     _check(lib, lib.x0ne_add_rmsnorm(_ptr(resid), _ptr(delta), _ptr(weight), _ptr(out), dtype_tag(out.dtype),
                                      _ptr(rows), n_rows, hidden, eps, _stream()), "add_rmsnorm")
+
+
+def add_normed_rmsnorm(resid: torch.Tensor, delta: torch.Tensor, delta_weight: torch.Tensor, delta_eps: float,
+                       weight: torch.Tensor, out: torch.Tensor, n_rows: int, eps: float,
+                       rows: Optional[torch.Tensor] = None) -> None:
+    """resid += rmsnorm(delta) * delta_weight (float32, never rounded); out = rmsnorm(resid) * weight.  `rows`
+    gathers source rows."""
+    lib = _lib("core")
+    hidden = weight.numel()
+    _need(resid, torch.float32, "residual")
+    _need(weight, torch.float32, "norm weight")
+    _need(delta_weight, torch.float32, "norm weight of the delta")
+    _need(out, out.dtype, "norm output")
+    _need(delta, out.dtype, "delta")
+    if delta.shape[-1] != hidden or delta_weight.numel() != hidden or resid.shape[-1] != hidden or out.shape[-1] != hidden \
+            or out.numel() < n_rows * hidden:
+        raise KernelError("add_normed_rmsnorm: widths differ or output too small")
+    if rows is not None:
+        _need(rows, torch.int32, "row list")
+        if rows.numel() < n_rows:
+            raise KernelError("add_normed_rmsnorm: row list shorter than the rows asked for")
+    elif resid.numel() < n_rows * hidden or delta.numel() < n_rows * hidden:
+        raise KernelError("add_normed_rmsnorm: residual or delta smaller than the rows asked for")
+    _check(lib, lib.x0ne_add_normed_rmsnorm(_ptr(resid), _ptr(delta), _ptr(delta_weight), delta_eps, _ptr(weight), _ptr(out),
+                                            dtype_tag(out.dtype), _ptr(rows), n_rows, hidden, eps, _stream()),
+           "add_normed_rmsnorm")
+
+
+def whole_norm_rope_kv_write(src: torch.Tensor, k_col: int, v_col: int, q_norm: torch.Tensor, k_norm: Optional[torch.Tensor],
+                             eps: float, freq: Optional[torch.Tensor], rot: int, table: Optional[torch.Tensor],
+                             q_out: torch.Tensor, q_heads: int, cache: PagedCacheArg, row_slot: torch.Tensor,
+                             row_pos: torch.Tensor, n_rows: int, write_kv: bool = True) -> None:
+    """Queries and keys normed over their whole projection (one weight per projected value), rotated (the
+    first `rot` values of every head, value i with i + rot/2), queries to `q_out`, keys and values into the
+    cache.  `src` rows hold the queries at column 0, the keys at k_col, the values at v_col; with
+    write_kv False only the queries are made (a layer that reads another layer's keys and values)."""
+    lib = _lib("core")
+    _need(src, src.dtype, "projection rows")
+    _need(q_out, src.dtype, "q output")
+    _need(row_slot, torch.int32, "row slots")
+    _need(row_pos, torch.int32, "row positions")
+    _need(q_norm, torch.float32, "q norm weight")
+    qn = q_heads * cache.head_dim
+    if q_norm.numel() != qn or q_out.shape[-1] != qn or q_out.numel() < n_rows * qn or src.numel() < n_rows * src.shape[-1]:
+        raise KernelError("whole_norm_rope: widths or rows do not match")
+    if write_kv:
+        _need(k_norm, torch.float32, "k norm weight")
+        if k_norm.numel() != cache.kv_heads * cache.head_dim:
+            raise KernelError("whole_norm_rope: the key norm weight does not match the key projection")
+    positions = 0
+    if rot:
+        _need(freq, torch.float32, "rotary frequencies")
+        if freq.numel() * 2 != rot:
+            raise KernelError("whole_norm_rope: frequencies are not rot / 2")
+        if table is not None:
+            _need(table, torch.float32, "rotary table")
+            if table.dim() != 2 or table.shape[1] != rot:
+                raise KernelError("whole_norm_rope: the table is not [positions, rot]")
+            positions = table.shape[0]
+    _check(lib, lib.x0ne_whole_norm_rope_kv_write(
+        _ptr(src), dtype_tag(src.dtype), src.shape[-1], k_col, v_col, _ptr(q_norm), _ptr(k_norm) if write_kv else None, eps,
+        _ptr(freq) if rot else None, rot, _ptr(table) if rot else None, positions, _ptr(q_out), q_heads, cache, _ptr(row_slot),
+        _ptr(row_pos), n_rows, 1 if write_kv else 0, _stream()), "whole_norm_rope_kv_write")
+
+
+def relu2(x: torch.Tensor, out: torch.Tensor, n_rows: int) -> None:
+    """out = max(x, 0)^2 on the first n_rows rows."""
+    lib = _lib("core")
+    _need(x, x.dtype, "activation input")
+    _need(out, x.dtype, "activation output")
+    width = x.shape[-1]
+    if out.shape[-1] != width or x.numel() < n_rows * width or out.numel() < n_rows * width:
+        raise KernelError("relu2: widths or rows do not match")
+    _check(lib, lib.x0ne_relu2(_ptr(x), _ptr(out), dtype_tag(x.dtype), n_rows * width, _stream()), "relu2")
+
+
+# ---------------------------------------------------------------------------------------------
+# routed feed-forward (csrc/moe.cu, module `core`; the tensor-core products in module `flex`)
+# ---------------------------------------------------------------------------------------------
+MOE_TILE_ROWS = 32       # pairs per tile of the grouped products (moe.cu: MOE_TILE_M)
+
+
+def moe_max_tiles(pairs: int, experts: int) -> int:
+    """Tiles a pass of `pairs` (row, choice) pairs over `experts` experts can need at most."""
+    full = pairs // MOE_TILE_ROWS + experts
+    return full if full < pairs else max(pairs, 1)
+
+
+def moe_route(z: torch.Tensor, correction: torch.Tensor, n: int, groups: int, keep: int, top: int, n_rows: int,
+              chosen: torch.Tensor, weights: torch.Tensor, sgate: Optional[torch.Tensor] = None, sg_col: int = 0) -> None:
+    """The router's choice per row from float32 logits z [rows, >= n] (see moe.cu): `chosen` int32 [rows, top],
+    `weights` float32 [rows, top]; `sgate` float32 [rows] = sigmoid(z[:, sg_col])."""
+    lib = _lib("core")
+    _need(z, torch.float32, "router logits")
+    _need(correction, torch.float32, "router correction")
+    _need(chosen, torch.int32, "chosen experts")
+    _need(weights, torch.float32, "choice weights")
+    if sgate is not None:
+        _need(sgate, torch.float32, "shared gate")
+    if correction.numel() != n or z.numel() < n_rows * z.shape[-1] or chosen.numel() < n_rows * top or weights.numel() < n_rows * top \
+            or (sgate is not None and sgate.numel() < n_rows):
+        raise KernelError("moe_route: buffers do not match the rows and choices asked for")
+    _check(lib, lib.x0ne_moe_route(_ptr(z), z.shape[-1], _ptr(correction), n, groups, keep, top, n_rows, _ptr(chosen),
+                                   _ptr(weights), _ptr(sgate), sg_col, _stream()), "moe_route")
+
+
+def moe_group(chosen: torch.Tensor, pairs: int, experts: int, offsets: torch.Tensor, listed: torch.Tensor,
+              tiles: torch.Tensor) -> None:
+    """Lists the pairs expert by expert and fills the table of tiles [max_tiles, 3] (expert, first place, count)."""
+    lib = _lib("core")
+    for t, what in ((chosen, "chosen experts"), (offsets, "expert offsets"), (listed, "listed pairs"), (tiles, "tile table")):
+        _need(t, torch.int32, what)
+    if chosen.numel() < pairs or listed.numel() < pairs or offsets.numel() < experts + 1:
+        raise KernelError("moe_group: buffers smaller than the pairs or experts asked for")
+    _check(lib, lib.x0ne_moe_group(_ptr(chosen), pairs, experts, _ptr(offsets), _ptr(listed), _ptr(tiles), tiles.numel() // 3,
+                                   _stream()), "moe_group")
+
+
+def moe_product(which: int, a: torch.Tensor, w: torch.Tensor, listed: torch.Tensor, tiles: torch.Tensor, n_tiles: int, top: int,
+                out: torch.Tensor) -> None:
+    """The experts' products over the first n_tiles tiles.  which 0: out[pair] = relu(x[pair // top] W_e^T)^2 in the
+    activation type; which 1: out[pair] = act[pair] W_e^T in float32.  w is [experts, N, K]."""
+    _need(a, w.dtype, "expert input")
+    _need(w, w.dtype, "expert weights")
+    _need(out, torch.float32 if which == 1 else w.dtype, "expert output")
+    _need(listed, torch.int32, "listed pairs")
+    _need(tiles, torch.int32, "tile table")
+    if w.dim() != 3 or a.shape[-1] != w.shape[2] or out.shape[-1] != w.shape[1] or tiles.numel() < 3 * n_tiles:
+        raise KernelError("moe_product: shapes do not match")
+    n, k = w.shape[1], w.shape[2]
+    if w.dtype == torch.bfloat16 and moe_tc_takes(n, k):
+        lib = _lib("flex")
+        _check(lib, lib.x0ne_moe_product_bf16(which, _ptr(a), a.shape[-1], _ptr(w), n, k, _ptr(listed), _ptr(tiles), n_tiles,
+                                              top, _ptr(out), _stream()), "moe_product_bf16")
+        return
+    lib = _lib("core")
+    _check(lib, lib.x0ne_moe_product(which, _ptr(a), a.shape[-1], _ptr(w), dtype_tag(w.dtype), n, k, _ptr(listed), _ptr(tiles),
+                                     n_tiles, top, _ptr(out), _stream()), "moe_product")
+
+
+def moe_tc_takes(n: int, k: int) -> bool:
+    """Whether the tensor-core kernel of the experts' products takes weights [n, k]."""
+    return MOE_TC and n % 8 == 0 and k % 16 == 0
+
+
+MOE_TC = False
+
+
+def moe_combine(y: torch.Tensor, x: torch.Tensor, chosen: torch.Tensor, weights: torch.Tensor, top: int, experts: int,
+                shared: Optional[torch.Tensor], sgate: Optional[torch.Tensor], out: torch.Tensor, n_rows: int) -> None:
+    """out[row] = sum_j weights[row, j] (y[row * top + j], or x[row] where chosen[row, j] >= experts)
+    + sgate[row] * shared[row], in float32."""
+    lib = _lib("core")
+    _need(y, torch.float32, "expert outputs")
+    _need(x, x.dtype, "rows")
+    _need(out, x.dtype, "feed-forward output")
+    hidden = x.shape[-1]
+    if y.shape[-1] != hidden or out.shape[-1] != hidden or y.numel() < n_rows * top * hidden or out.numel() < n_rows * hidden:
+        raise KernelError("moe_combine: widths or rows do not match")
+    if shared is not None:
+        _need(shared, x.dtype, "shared expert output")
+    _check(lib, lib.x0ne_moe_combine(_ptr(y), _ptr(x), dtype_tag(x.dtype), _ptr(chosen), _ptr(weights), top, experts,
+                                     _ptr(shared), _ptr(sgate), _ptr(out), n_rows, hidden, _stream()), "moe_combine")
 
 
 def qk_norm_rope_kv_write(qkv: torch.Tensor, q_norm: Optional[torch.Tensor], k_norm: Optional[torch.Tensor],

@@ -2,17 +2,19 @@
 from .base import (BLOCKS, EMBEDDINGS, FEED_FORWARDS, HEADS, MIXERS, NORMS, PART_REGISTRIES, POSITIONS, Block, BuildEnv,
                    CacheNeed, Embedding, FeedForward, Head, Mixer, Norm, Part, PositionEncoding, Registry)
 from .linear import Linear
-from . import attention, block, embedding, latent_attention, masked_attention, mlp, norm, rope  # noqa: F401  (registers the built-in parts)
+from . import attention, block, embedding, latent_attention, masked_attention, mlp, moe, norm, rope, window_attention  # noqa: F401  (registers the built-in parts)
 from .attention import GQAttention
-from .block import ParallelBlock, PreNormBlock
+from .block import ParallelBlock, PreNormBlock, SandwichBlock
 from .latent_attention import LatentAttention
 from .masked_attention import MaskedAttention
 from .embedding import LMHead, TokenEmbedding
 from .mlp import ClippedGLU, SwiGLU
-from .norm import RMSNorm
+from .moe import RoutedExperts
+from .norm import PostNormed, RMSNorm
+from .window_attention import SinkWindowAttention
 from .rope import NoPosition, Rope, YarnRope, inv_freq_f32, yarn_frequencies
 
 __all__ = ["BLOCKS", "EMBEDDINGS", "FEED_FORWARDS", "HEADS", "MIXERS", "NORMS", "PART_REGISTRIES", "POSITIONS", "Block",
            "BuildEnv", "CacheNeed", "Embedding", "FeedForward", "Head", "Mixer", "Norm", "Part", "PositionEncoding",
            "Registry", "Linear", "GQAttention",
-           "PreNormBlock", "ParallelBlock", "MaskedAttention", "LatentAttention", "ClippedGLU", "YarnRope", "yarn_frequencies", "LMHead", "TokenEmbedding", "SwiGLU", "RMSNorm", "NoPosition", "Rope", "inv_freq_f32"]
+           "PreNormBlock", "ParallelBlock", "SandwichBlock", "SinkWindowAttention", "RoutedExperts", "PostNormed", "MaskedAttention", "LatentAttention", "ClippedGLU", "YarnRope", "yarn_frequencies", "LMHead", "TokenEmbedding", "SwiGLU", "RMSNorm", "NoPosition", "Rope", "inv_freq_f32"]

@@ -73,7 +73,7 @@ def run_attention_ex(ctx, q, out, view, n_rows, q_heads, scale, window, extra):
     if not ops.attention_flex_takes(view, q.dtype, extra.v_from_k, ctx.decode):
         ops.attention_rows(q, out, view, ctx.row_slot, ctx.row_pos, n_rows, q_heads, scale, window, extra)
     elif ctx.decode:
-        visible = min(v for v in (ctx.max_context, extra.chunk, window) if v)
+        visible = min(v for v in (ctx.max_context, extra.chunk, window + extra.keep_first if window else 0) if v)
         splits = flex_decode_splits(ctx, n_rows, view.kv_heads, q_heads, visible)
         scratch = None
         if splits > 1:

@@ -14,13 +14,14 @@ from .linear import Linear
 
 class TokenEmbedding(Embedding):
     """resid[r] = float32(table[token[r]]); an id outside the table gives a zero row
-    (x0ne-core/kernels/cuda/embedding.cu:5-17).  Parameters: vocab_size, hidden_size,
-    names.weight."""
+    (x0ne-core/kernels/cuda/embedding.cu:5-17).  With `scale` the row is multiplied by it in float32
+    on its way into the residual.  Parameters: vocab_size, hidden_size, scale (default 1), names.weight."""
     replayable = True
 
     def __init__(self, spec, env):
         super().__init__(spec, env)
         self.table = None
+        self.scale = float(spec.get("scale", 1.0) or 1.0)
 
     @staticmethod
     def tensor_needs(spec: PartSpec) -> List[TensorNeed]:
@@ -31,7 +32,7 @@ class TokenEmbedding(Embedding):
         self.table = tensors[self.spec["names"]["weight"]]
 
     def forward(self, ctx, resid, n_rows):
-        ops.embedding(self.table, ctx.tokens, resid, n_rows)
+        ops.embedding(self.table, ctx.tokens, resid, n_rows, self.scale)
 
 
 class LMHead(Head):

@@ -1,0 +1,125 @@
+"""Routed feed-forward: a router picks a few small experts per row; a shared expert may run beside them."""
+from __future__ import annotations
+
+from typing import List, Mapping
+
+import torch
+
+from ..config.spec import PartSpec
+from ..csrc import ops
+from ..weights.loader import TensorNeed
+from .base import FEED_FORWARDS, FeedForward
+from .linear import Linear
+
+
+class RoutedExperts(FeedForward):
+    """out = sum over the row's chosen experts of weight_e expert_e(x)  (+ sigmoid(w_g . x) shared(x)).
+
+    Router: float32 logits z = x W_r^T over `experts` + `identity` outputs; scores s = softmax(z); the
+    choice is made on s + correction: the outputs form `groups` equal groups of neighbours, a group
+    is worth its largest such value, only the `keep_groups` best groups can give experts, and of
+    those the `top` largest values are chosen; the weights are the chosen outputs' scores s, not
+    renormalized.  An expert is down(act(up x)) with act the squared ReLU, no biases.  The last
+    `identity` router outputs are identity experts: they return x itself and have no tensors.  The
+    shared expert has the same form with a width of its own, runs for every row, and is multiplied
+    by the sigmoid of one more projection of x (`shared_gate`).
+
+    One product gives the router logits and the shared gate's logit (float32); a kernel makes the
+    choice; the (row, choice) pairs are listed expert by expert on the device and both products of the
+    experts run over tiles of one expert's pairs (`ops.moe_product`), so the host never learns who
+    chose what and the launches replay from a graph.  The sum is taken in float32 in the order of
+    the choices.
+
+    Parameters: hidden_size, experts, identity, top, groups, keep_groups, expert_size, activation
+    ("relu2"), shared_size (None: no shared expert), shared_gate, names.{router, correction, up, down
+    (patterns with {e}), shared_up, shared_down, shared_gate}.
+    """
+    replayable = True
+
+    def __init__(self, spec, env):
+        super().__init__(spec, env)
+        g = spec.get
+        self.hidden = int(spec["hidden_size"])
+        self.experts = int(spec["experts"])
+        self.identity = int(g("identity") or 0)
+        self.n_out = self.experts + self.identity
+        self.top = int(spec["top"])
+        self.groups = int(g("groups") or 1)
+        self.keep_groups = int(g("keep_groups") or self.groups)
+        self.inter = int(spec["expert_size"])
+        self.shared_size = int(g("shared_size") or 0)
+        self.shared_gate = bool(g("shared_gate")) and self.shared_size > 0
+        if g("activation", "relu2") != "relu2":
+            raise ValueError(f"expert activation {g('activation')!r} is not served; served: 'relu2'")
+        if self.n_out % self.groups or not 1 <= self.keep_groups <= self.groups or \
+                not 1 <= self.top <= self.keep_groups * (self.n_out // self.groups):
+            raise ValueError(f"{self.n_out} router outputs in {self.groups} groups of which {self.keep_groups} stay cannot "
+                             f"give {self.top} choices")
+        self.router = self.correction = self.up = self.down = self.shared_up = self.shared_down = None
+
+    @staticmethod
+    def tensor_needs(spec: PartSpec) -> List[TensorNeed]:
+        h, n = int(spec["hidden_size"]), spec["names"]
+        E, I, ff = int(spec["experts"]), int(spec.get("identity") or 0), int(spec["expert_size"])
+        needs = []
+        for e in range(E):
+            needs += [TensorNeed(n["up"].format(e=e), (ff, h)), TensorNeed(n["down"].format(e=e), (h, ff))]
+        needs += [TensorNeed(n["router"], (E + I, h)), TensorNeed(n["correction"], (E + I,), role="vector", init="linear")]
+        sf = int(spec.get("shared_size") or 0)
+        if sf:
+            needs += [TensorNeed(n["shared_up"], (sf, h)), TensorNeed(n["shared_down"], (h, sf))]
+            if spec.get("shared_gate"):
+                needs.append(TensorNeed(n["shared_gate"], (1, h)))
+        return needs
+
+    def bind(self, tensors: Mapping[str, torch.Tensor]) -> None:
+        n = self.spec["names"]
+        rows = [tensors[n["router"]]] + ([tensors[n["shared_gate"]]] if self.shared_gate else [])
+        self.router = Linear(torch.cat(rows, dim=0).contiguous())
+        self.correction = tensors[n["correction"]]
+        self.up = torch.stack([tensors[n["up"].format(e=e)] for e in range(self.experts)]).contiguous()       # [E, ff, hidden]
+        self.down = torch.stack([tensors[n["down"].format(e=e)] for e in range(self.experts)]).contiguous()   # [E, hidden, ff]
+        if self.shared_size:
+            self.shared_up = Linear(tensors[n["shared_up"]])
+            self.shared_down = Linear(tensors[n["shared_down"]])
+
+    def weight_bytes(self) -> int:
+        """A step reads the router, the shared expert, and at most `top` experts per row; counted here for one row."""
+        per_expert = (self.up[0].numel() + self.down[0].numel()) * self.up.element_size()
+        total = self.router.weight_bytes() + min(self.top, self.experts) * per_expert
+        if self.shared_size:
+            total += self.shared_up.weight_bytes() + self.shared_down.weight_bytes()
+        return total
+
+    def forward(self, ctx, x, n_rows):
+        dt, rows, top = self.env.dtype, ctx.ws.max_rows, self.top
+        ws = ctx.ws
+        z = ws.buffer("moe.logits", (rows, self.router.out_features), torch.float32)
+        chosen = ws.buffer("moe.chosen", (rows, top), torch.int32)
+        weights = ws.buffer("moe.weights", (rows, top), torch.float32)
+        sgate = ws.buffer("moe.shared_gate", (rows,), torch.float32) if self.shared_gate else None
+        offsets = ws.buffer("moe.offsets", (self.experts + 1,), torch.int32)
+        listed = ws.buffer("moe.listed", (rows * top,), torch.int32)
+        tiles = ws.buffer("moe.tiles", (ops.moe_max_tiles(rows * top, self.experts), 3), torch.int32)
+        act = ws.buffer("moe.act", (rows * top, self.inter), dt)
+        y = ws.buffer("moe.y", (rows * top, self.hidden), torch.float32)
+        out = ws.buffer(self.out_buffer, (rows, self.hidden), dt)
+        self.router(x, z, n_rows)
+        ops.moe_route(z, self.correction, self.n_out, self.groups, self.keep_groups, top, n_rows, chosen, weights, sgate, self.n_out)
+        pairs = n_rows * top
+        n_tiles = ops.moe_max_tiles(pairs, self.experts)
+        ops.moe_group(chosen, pairs, self.experts, offsets, listed, tiles[:n_tiles])
+        ops.moe_product(0, x, self.up, listed, tiles, n_tiles, top, act)
+        ops.moe_product(1, act, self.down, listed, tiles, n_tiles, top, y)
+        shared = None
+        if self.shared_size:
+            su = ws.buffer("moe.shared_up", (rows, self.shared_size), dt)
+            shared = ws.buffer("moe.shared_out", (rows, self.hidden), dt)
+            self.shared_up(x, su, n_rows)
+            ops.relu2(su, su, n_rows)
+            self.shared_down(su, shared, n_rows)
+        ops.moe_combine(y, x, chosen, weights, top, self.experts, shared, sgate, out, n_rows)
+        return out
+
+
+FEED_FORWARDS.register("routed_experts", RoutedExperts)

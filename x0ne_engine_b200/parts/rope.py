@@ -22,8 +22,10 @@ class Rope(PositionEncoding):
     """Rotate-half RoPE over the first `rotary_dim` values of each head: the pair
     (i, i + rotary_dim/2) turns by pos * inv_freq[i] (x0ne-core/kernels/cuda/rope.cu:28-31).
     The rotation itself runs inside the mixer's fused kernel; this part owns the table.
-    Parameters: head_dim, rotary_dim, theta."""
+    Parameters: head_dim, rotary_dim, theta, freq_in_double (default False: the frequencies are worked
+    out in float32 from a float32 theta; True: in float64, then narrowed once)."""
     replayable = True
+    TABLE_POSITIONS = 1 << 16      # the table covers this many positions at most; kernels compute the rest
 
     def __init__(self, spec, env):
         super().__init__(spec, env)
@@ -32,7 +34,11 @@ class Rope(PositionEncoding):
         if self.rotary_dim % 2 or not 0 < self.rotary_dim <= self.head_dim:
             raise ValueError(f"rotary_dim {self.rotary_dim} must be even and at most head_dim {self.head_dim}")
         self.theta = float(spec["theta"])
-        self.inv_freq = inv_freq_f32(self.rotary_dim, self.theta)
+        if spec.get("freq_in_double"):
+            i = np.arange(self.rotary_dim // 2, dtype=np.float64)
+            self.inv_freq = np.power(self.theta, -2.0 * i / self.rotary_dim).astype(np.float32)
+        else:
+            self.inv_freq = inv_freq_f32(self.rotary_dim, self.theta)
         self.table = torch.from_numpy(self.inv_freq).to(env.device)
         self._cos_sin = None
 
@@ -43,6 +49,7 @@ class Rope(PositionEncoding):
         """float32 [positions, rotary_dim]: cos then sin of the float32 angle position * inv_freq[i],
         made once on the host; mixers pass it to the fused kernel so that it reads two short rows
         instead of computing the row's sines and cosines for every head."""
+        positions = max(1, min(int(positions), self.TABLE_POSITIONS))
         if self._cos_sin is None or self._cos_sin.shape[0] < positions:
             pos = np.arange(positions, dtype=np.float32)[:, None]
             ang = (pos * self.inv_freq[None, :]).astype(np.float32).astype(np.float64)
