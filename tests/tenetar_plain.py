@@ -107,8 +107,9 @@ def relu2_expert(h: torch.Tensor, w: Mapping[str, torch.Tensor], prefix: str) ->
     return torch.relu(h @ f32(w[prefix + "up"]).T).square() @ f32(w[prefix + "down"]).T
 
 
-def route(h: torch.Tensor, router: Mapping, w: Mapping[str, torch.Tensor], prefix: str):
-    """(chosen [T, k] expert indices, weights [T, k]).  Scores are the softmax over all E + I router outputs;
+def route(h: torch.Tensor, router: Mapping, w: Mapping[str, torch.Tensor], prefix: str, margins: Optional[list] = None):
+    """(chosen [T, k] expert indices, weights [T, k]).  `margins` collects, per token, how far the choice was
+    from going another way (the gap between the last group or expert taken and the first one left).  Scores are the softmax over all E + I router outputs;
     the choice is made on score + correction, among the experts of the `keep` groups whose best such value
     is largest (all others count as minus infinity); the weights are the plain scores of the chosen."""
     z = h @ f32(w[prefix + "router"]).T
@@ -123,13 +124,22 @@ def route(h: torch.Tensor, router: Mapping, w: Mapping[str, torch.Tensor], prefi
     allowed = kept.repeat_interleave(n // count, dim=1)
     choice = choice.masked_fill(~allowed, float("-inf"))
     chosen = choice.topk(router["top"], dim=-1).indices
+    if margins is not None:
+        gap = torch.full((h.shape[0],), float("inf"))
+        if keep < count:
+            b = best.sort(dim=-1, descending=True).values
+            gap = torch.minimum(gap, b[:, keep - 1] - b[:, keep])
+        c = choice.sort(dim=-1, descending=True).values
+        if router["top"] < n:
+            gap = torch.minimum(gap, c[:, router["top"] - 1] - c[:, router["top"]])
+        margins.append(gap)
     return chosen, s.gather(1, chosen)
 
 
-def moe_ff(h: torch.Tensor, mlp: Mapping, w: Mapping[str, torch.Tensor], prefix: str) -> torch.Tensor:
+def moe_ff(h: torch.Tensor, mlp: Mapping, w: Mapping[str, torch.Tensor], prefix: str, margins: Optional[list] = None) -> torch.Tensor:
     router = mlp["router"]
     E, I = router["experts"], router.get("identity", 0)
-    chosen, weights = route(h, router, w, prefix)
+    chosen, weights = route(h, router, w, prefix, margins)
     out = torch.zeros_like(h)
     for t in range(h.shape[0]):
         for e, g in zip(chosen[t].tolist(), weights[t]):
@@ -142,8 +152,10 @@ def moe_ff(h: torch.Tensor, mlp: Mapping, w: Mapping[str, torch.Tensor], prefix:
     return out
 
 
-def forward(config: Mapping, w: Mapping[str, torch.Tensor], tokens: List[int], layers_out: Optional[list] = None) -> torch.Tensor:
-    """Logits [T, vocab] of a whole sequence; `layers_out` collects the residual stream after every layer."""
+def forward(config: Mapping, w: Mapping[str, torch.Tensor], tokens: List[int], layers_out: Optional[list] = None,
+            margins: Optional[list] = None) -> torch.Tensor:
+    """Logits [T, vocab] of a whole sequence; `layers_out` collects the residual stream after every layer,
+    `margins` the routers' margins (see `route`)."""
     eps = float(config["norm"]["eps"])
     T = len(tokens)
     positions = torch.arange(T)
@@ -161,7 +173,7 @@ def forward(config: Mapping, w: Mapping[str, torch.Tensor], tokens: List[int], l
         mlp = layer.get("mlp")
         if mlp is not None:
             h = rms_norm(x, f32(w[p + "norm2"]), eps)
-            y = dense_ff(h, w, p + "mlp.") if mlp["kind"] == "dense" else moe_ff(h, mlp, w, p + "mlp.")
+            y = dense_ff(h, w, p + "mlp.") if mlp["kind"] == "dense" else moe_ff(h, mlp, w, p + "mlp.", margins)
             x = x + rms_norm(y, f32(w[p + "norm2b"]), eps)
         if layers_out is not None:
             layers_out.append(x.clone())
