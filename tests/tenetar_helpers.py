@@ -17,6 +17,8 @@ import torch
 
 import tenetar_plain as P
 
+P.PRECISION = torch.float64      # the reference of the tests is the plain implementation in double precision
+
 
 def attention(dim=20, heads=6, kv_heads=2, vdim=12, window=37, keep=3, rot=12, base=10000.0, scale=None, kv_from=None):
     m = {"dim": dim, "heads": heads, "kv_heads": kv_heads, "vdim": vdim, "scale": scale or 1.3 * dim ** -0.5}
@@ -78,13 +80,13 @@ CONFIGS = {
 _folders = {}
 
 
-def make_tensors(cfg: dict, seed: int, sharp: float = 1.0, router_scale: float = 40.0, spaced: float = 0.11):
+def make_tensors(cfg: dict, seed: int, sharp: float = 1.0, router_scale: float = 6.0, spaced: float = 0.4):
     """Random tensors by name (float32 values that bfloat16 holds exactly).  `sharp` scales the query
     projections, which makes the softmax peaky: single keys then decide the output.  `router_scale`
     spreads the router's logits and `spaced` puts the corrections this far apart (in a random order, some
-    negative), so that few choices are close calls: the row's strongest output decides which group and
-    expert come first, the corrections the rest.  spaced = 0 draws the corrections at random (close calls
-    are then common, and only a float32 run follows the plain implementation through them)."""
+    negative; a score near 1 lands half way between two of them); spaced = 0 draws them at random.  Close
+    calls between two choices are common either way: a float32 run follows the plain implementation through
+    them, a bfloat16 run is compared under its own choices (`Choices`)."""
     g = torch.Generator().manual_seed(seed)
 
     def mat(o, i, s=1.0):
@@ -157,8 +159,87 @@ def folder(name: str, seed: int = 0, sharp: float = 1.0, soft: bool = False):
     return _folders[key]
 
 
-def plain_logits(cfg, tensors, ids, layers_out=None, margins=None):
-    return P.forward(cfg, tensors, list(ids), layers_out, margins).numpy()
+def plain_logits(cfg, tensors, ids, layers_out=None, margins=None, forced=None):
+    return P.forward(cfg, tensors, list(ids), layers_out, margins, forced).numpy()
+
+
+class Choices:
+    """Records what the routers of an engine choose, per layer and (slot, position), while it is active.  A
+    bfloat16 run may take another expert than the plain implementation where two choices are within its
+    rounding, and from there on the two would differ altogether; the tests give the plain implementation
+    the engine's choices (`forced`) and check separately that the choices agree wherever they are clear.
+    (The engine must launch its passes itself, `pass_graphs=False`: a replayed graph calls no Python.)"""
+
+    def __init__(self, eng):
+        self.eng = eng
+        self.layers = [i for i, b in enumerate(eng.model.blocks) if type(getattr(b, "ffn", None)).__name__ == "RoutedExperts"]
+        self.seen = {i: {} for i in self.layers}
+
+    def __enter__(self):
+        for i in self.layers:
+            part = self.eng.model.blocks[i].ffn
+
+            def forward(ctx, x, n_rows, _f=type(part).forward, _p=part, _i=i):
+                out = _f(_p, ctx, x, n_rows)
+                top = _p.top
+                ch = ctx.ws.buffer("moe.chosen", (ctx.ws.max_rows, top), torch.int32)[:n_rows].cpu()
+                slots, pos = ctx.row_slot[:n_rows].cpu().tolist(), ctx.row_pos[:n_rows].cpu().tolist()
+                for r, (s, p) in enumerate(zip(slots, pos)):
+                    if s >= 0:
+                        self.seen[_i][(s, p)] = ch[r].clone()
+                return out
+            part.forward = forward
+        return self
+
+    def __exit__(self, *exc):
+        for i in self.layers:
+            del self.eng.model.blocks[i].ffn.forward
+
+    def of(self, slot: int, n: int):
+        """{layer: [n, k]} for positions 0..n-1 of the sequence that ran in `slot`."""
+        return {i: torch.stack([self.seen[i][(slot, p)] for p in range(n)]) for i in self.layers}
+
+
+def agreement(cfg, tensors, ids, forced, clear=0.25):
+    """(fraction of (token, layer) whose engine choice equals the plain choice, the same among those where the
+    plain margin is at least `clear`)."""
+    layers = [i for i, l in enumerate(cfg["layers"]) if l.get("mlp") and l["mlp"]["kind"] == "moe"]
+    same_all, same_clear, n_clear, n_all = 0, 0, 0, 0
+    # the plain run follows the engine's choices, so that every router sees the inputs the engine's router saw
+    hs = plain_router_inputs(cfg, tensors, ids, forced)
+    for k, i in enumerate(layers):
+        mlp = cfg["layers"][i]["mlp"]
+        m = []
+        chosen, _ = P.route(hs[i], mlp["router"], tensors, f"l{i}.mlp.", m)
+        eq = (chosen.sort(-1).values == forced[i].to(torch.long).sort(-1).values).all(-1)
+        ok = m[0] >= clear
+        same_all += int(eq.sum()); n_all += eq.numel()
+        same_clear += int((eq & ok).sum()); n_clear += int(ok.sum())
+    return same_all / max(n_all, 1), same_clear / max(n_clear, 1)
+
+
+def plain_router_inputs(cfg, tensors, ids, forced):
+    """{layer: the normed rows its feed-forward reads} of the plain run that follows `forced`."""
+    out, eps = {}, float(cfg["norm"]["eps"])
+    layers_out = []
+    P.forward(cfg, tensors, list(ids), layers_out, None, forced)
+    # the input of layer i's feed-forward is the residual after its mixer: recomputed from the residual
+    # before the layer by running the layer's mixer part again
+    x = P.f32(tensors["embed"])[torch.tensor(list(ids))] * float(cfg["embedding"]["scale"])
+    positions = torch.arange(len(ids))
+    kept = {}
+    for i, layer in enumerate(cfg["layers"]):
+        p, mixer = f"l{i}.", layer["mixer"]
+        h = P.rms_norm(x, P.f32(tensors[p + "norm1"]), eps)
+        if mixer.get("kv_from") is not None:
+            kv = kept[mixer["kv_from"]]
+        else:
+            kv = kept[i] = P.attention_keys_values(h, mixer, tensors, p + "mix.", eps, positions)
+        x_mid = x + P.rms_norm(P.attention_mixer(h, mixer, tensors, p + "mix.", eps, positions, kv), P.f32(tensors[p + "norm1b"]), eps)
+        if layer.get("mlp") is not None:
+            out[i] = P.rms_norm(x_mid, P.f32(tensors[p + "norm2"]), eps)
+        x = layers_out[i]
+    return out
 
 
 def clear_ids(cfg, tensors, n, seed=0, margin=0.0):

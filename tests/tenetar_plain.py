@@ -16,8 +16,12 @@ from typing import Dict, List, Mapping, Optional
 import torch
 
 
+PRECISION = torch.float32      # the tests set float64: the same equations, as a sharper reference
+
+
 def f32(t: torch.Tensor) -> torch.Tensor:
-    return t.detach().to("cpu", torch.float32)
+    """The tensor on the CPU in the working precision (float32 unless PRECISION says otherwise)."""
+    return t.detach().to("cpu", PRECISION)
 
 
 def rms_norm(x: torch.Tensor, w: torch.Tensor, eps: float) -> torch.Tensor:
@@ -32,8 +36,8 @@ def rotate_half_layout(x: torch.Tensor, positions: torch.Tensor, dims: int, base
         return x
     half = dims // 2
     i = torch.arange(half, dtype=torch.float64)
-    freq = torch.pow(torch.tensor(float(base), dtype=torch.float64), -2.0 * i / dims).to(torch.float32)
-    ang = positions.to(torch.float32)[:, None] * freq[None, :]             # [T, half]
+    freq = torch.pow(torch.tensor(float(base), dtype=torch.float64), -2.0 * i / dims).to(torch.float32).to(PRECISION)
+    ang = positions.to(PRECISION)[:, None] * freq[None, :]             # [T, half]
     c, s = torch.cos(ang)[:, None, :], torch.sin(ang)[:, None, :]
     u, v = x[..., :half], x[..., half:dims]
     return torch.cat([u * c - v * s, v * c + u * s, x[..., dims:]], dim=-1)
@@ -107,7 +111,8 @@ def relu2_expert(h: torch.Tensor, w: Mapping[str, torch.Tensor], prefix: str) ->
     return torch.relu(h @ f32(w[prefix + "up"]).T).square() @ f32(w[prefix + "down"]).T
 
 
-def route(h: torch.Tensor, router: Mapping, w: Mapping[str, torch.Tensor], prefix: str, margins: Optional[list] = None):
+def route(h: torch.Tensor, router: Mapping, w: Mapping[str, torch.Tensor], prefix: str, margins: Optional[list] = None,
+          forced: Optional[torch.Tensor] = None):
     """(chosen [T, k] expert indices, weights [T, k]).  `margins` collects, per token, how far the choice was
     from going another way (the gap between the last group or expert taken and the first one left).  Scores are the softmax over all E + I router outputs;
     the choice is made on score + correction, among the experts of the `keep` groups whose best such value
@@ -125,7 +130,7 @@ def route(h: torch.Tensor, router: Mapping, w: Mapping[str, torch.Tensor], prefi
     choice = choice.masked_fill(~allowed, float("-inf"))
     chosen = choice.topk(router["top"], dim=-1).indices
     if margins is not None:
-        gap = torch.full((h.shape[0],), float("inf"))
+        gap = torch.full((h.shape[0],), float("inf"), dtype=h.dtype)
         if keep < count:
             b = best.sort(dim=-1, descending=True).values
             gap = torch.minimum(gap, b[:, keep - 1] - b[:, keep])
@@ -133,13 +138,16 @@ def route(h: torch.Tensor, router: Mapping, w: Mapping[str, torch.Tensor], prefi
         if router["top"] < n:
             gap = torch.minimum(gap, c[:, router["top"] - 1] - c[:, router["top"]])
         margins.append(gap)
+    if forced is not None:          # the choice is given (a run in lower precision made it); the weights stay this run's scores
+        chosen = forced.to(torch.long)
     return chosen, s.gather(1, chosen)
 
 
-def moe_ff(h: torch.Tensor, mlp: Mapping, w: Mapping[str, torch.Tensor], prefix: str, margins: Optional[list] = None) -> torch.Tensor:
+def moe_ff(h: torch.Tensor, mlp: Mapping, w: Mapping[str, torch.Tensor], prefix: str, margins: Optional[list] = None,
+           forced: Optional[torch.Tensor] = None) -> torch.Tensor:
     router = mlp["router"]
     E, I = router["experts"], router.get("identity", 0)
-    chosen, weights = route(h, router, w, prefix, margins)
+    chosen, weights = route(h, router, w, prefix, margins, forced)
     out = torch.zeros_like(h)
     for t in range(h.shape[0]):
         for e, g in zip(chosen[t].tolist(), weights[t]):
@@ -153,9 +161,10 @@ def moe_ff(h: torch.Tensor, mlp: Mapping, w: Mapping[str, torch.Tensor], prefix:
 
 
 def forward(config: Mapping, w: Mapping[str, torch.Tensor], tokens: List[int], layers_out: Optional[list] = None,
-            margins: Optional[list] = None) -> torch.Tensor:
+            margins: Optional[list] = None, forced: Optional[Mapping[int, torch.Tensor]] = None) -> torch.Tensor:
     """Logits [T, vocab] of a whole sequence; `layers_out` collects the residual stream after every layer,
-    `margins` the routers' margins (see `route`)."""
+    `margins` the routers' margins (see `route`); `forced` gives, for layers by index, the experts every
+    token takes ([T, k]) instead of the router's own choice."""
     eps = float(config["norm"]["eps"])
     T = len(tokens)
     positions = torch.arange(T)
@@ -173,7 +182,7 @@ def forward(config: Mapping, w: Mapping[str, torch.Tensor], tokens: List[int], l
         mlp = layer.get("mlp")
         if mlp is not None:
             h = rms_norm(x, f32(w[p + "norm2"]), eps)
-            y = dense_ff(h, w, p + "mlp.") if mlp["kind"] == "dense" else moe_ff(h, mlp, w, p + "mlp.", margins)
+            y = dense_ff(h, w, p + "mlp.") if mlp["kind"] == "dense" else moe_ff(h, mlp, w, p + "mlp.", margins, (forced or {}).get(i))
             x = x + rms_norm(y, f32(w[p + "norm2b"]), eps)
         if layers_out is not None:
             layers_out.append(x.clone())

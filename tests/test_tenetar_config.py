@@ -97,17 +97,17 @@ def test_plain_mask_and_sink():
     assert m[11].tolist() == [True, True] + [False] * 6 + [True] * 4
     assert m[3].tolist() == [True] * 4 + [False] * 8 and m[5, 1] and not m[6, 2] and m[6, 3]
     assert P.visible(5, None, 0).tolist() == torch.tril(torch.ones(5, 5, dtype=torch.bool)).tolist()
-    s = torch.zeros(1, 1, 3)
-    p = P.sink_softmax(s, torch.ones(1, 3, dtype=torch.bool), torch.tensor([0.0]))
-    assert torch.allclose(p, torch.full((1, 1, 3), 0.25))        # three keys and the sink share the denominator
-    assert torch.allclose(P.sink_softmax(s, torch.ones(1, 3, dtype=torch.bool), None), torch.full((1, 1, 3), 1 / 3))
+    s = torch.zeros(1, 1, 3, dtype=torch.float64)
+    p = P.sink_softmax(s, torch.ones(1, 3, dtype=torch.bool), torch.tensor([0.0], dtype=torch.float64))
+    assert torch.allclose(p, torch.full((1, 1, 3), 0.25, dtype=torch.float64))        # three keys and the sink share the denominator
+    assert torch.allclose(P.sink_softmax(s, torch.ones(1, 3, dtype=torch.bool), None), torch.full((1, 1, 3), 1 / 3, dtype=torch.float64))
 
 
 def test_plain_rotation_is_partial_and_relative():
-    x = torch.randn(4, 2, 10)
+    x = torch.randn(4, 2, 10, dtype=torch.float64)
     y = P.rotate_half_layout(x, torch.arange(4), 6, 100.0)
     assert torch.equal(y[..., 6:], x[..., 6:]) and torch.equal(y[0], x[0]) and not torch.allclose(y[1, :, :6], x[1, :, :6])
-    q, k = torch.randn(1, 1, 6), torch.randn(1, 1, 6)
+    q, k = torch.randn(1, 1, 6, dtype=torch.float64), torch.randn(1, 1, 6, dtype=torch.float64)
     dots = [float((P.rotate_half_layout(q, torch.tensor([p + 3]), 6, 100.0) * P.rotate_half_layout(k, torch.tensor([p]), 6, 100.0)).sum())
             for p in (0, 5, 40)]
     assert max(dots) - min(dots) < 1e-4
@@ -117,7 +117,7 @@ def test_plain_routing_rules():
     n, top = 8, 2
     router = {"experts": 6, "identity": 2, "top": top, "groups": {"count": 4, "keep": 2}}
     w = {"r.router": torch.eye(n), "r.correction": torch.tensor([0., 0., 0., 0., 0., 0., 0., -5.0])}
-    z = torch.tensor([[0., 0., 3., 2.9, 0., 0., 2.95, 6.0]])          # output 7 has the largest score but a large negative correction
+    z = torch.tensor([[0., 0., 3., 2.9, 0., 0., 2.95, 6.0]], dtype=torch.float64)          # output 7 has the largest score but a large negative correction
     chosen, weights = P.route(z, router, w, "r.")
     s = torch.softmax(z, -1)[0]
     # groups are (0,1) (2,3) (4,5) (6,7): the best two by choice value are (2,3) and (6,7) (through output 6)
@@ -134,14 +134,19 @@ def test_plain_identity_expert_and_shared_gate():
     cfg = H.CONFIGS["experts_only"]()
     t = H.make_tensors(cfg, 1)
     mlp = cfg["layers"][0]["mlp"]
-    h = torch.randn(5, cfg["width"])
+    h = torch.randn(5, cfg["width"], dtype=torch.float64)
     base = P.moe_ff(h, mlp, t, "l0.mlp.")
     t2 = dict(t)
-    t2["l0.mlp.shared.sg"] = t["l0.mlp.shared.sg"] * 0 - 1e4         # gate closed: the shared expert vanishes
+    t2["l0.mlp.shared.down"] = t["l0.mlp.shared.down"] * 0           # the shared expert vanishes
     closed = P.moe_ff(h, mlp, t2, "l0.mlp.")
     assert not torch.allclose(base, closed)
     no_shared = {**mlp, "shared": None}
-    assert torch.allclose(P.moe_ff(h, no_shared, t, "l0.mlp."), closed, atol=1e-6)
+    assert torch.allclose(P.moe_ff(h, no_shared, t, "l0.mlp."), closed, atol=1e-9)
+    # the gate is one number per row: halving it everywhere (sg = 0) halves the shared part
+    t4 = dict(t)
+    t4["l0.mlp.shared.sg"] = t["l0.mlp.shared.sg"] * 0
+    gate = torch.sigmoid(h @ t["l0.mlp.shared.sg"].double().T)
+    assert torch.allclose(P.moe_ff(h, mlp, t4, "l0.mlp.") - closed, (base - closed) * 0.5 / gate, atol=1e-9)
     # a row that chooses only identity experts gets itself times the sum of its weights
     t3 = dict(t2)
     t3["l0.mlp.correction"] = torch.tensor([-9.0] * 6 + [5.0, 5.0])

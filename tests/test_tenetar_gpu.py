@@ -17,12 +17,14 @@ pytestmark = pytest.mark.gpu
 
 DTYPES = ["float32", "bfloat16"]
 DEV = "cuda:0"
-MARGIN = {"float32": 1e-4, "bfloat16": 0.03}
+MARGIN = {"float32": 1e-4, "bfloat16": 0.0}
 _engines = {}
 
 
 def engine(name, dtype, seed=0, sharp=1.0, soft=False, max_tokens=2048, **kw):
     from x0ne_engine_b200 import Engine
+    if dtype == "bfloat16":
+        kw.setdefault("pass_graphs", False)          # the routers' choices are recorded by Python hooks (H.Choices)
     key = (name, dtype, seed, sharp, soft, max_tokens, tuple(sorted(kw.items())))
     if key not in _engines:
         folder, cfg, tensors = H.folder(name, seed, sharp, soft)
@@ -30,44 +32,76 @@ def engine(name, dtype, seed=0, sharp=1.0, soft=False, max_tokens=2048, **kw):
     return _engines[key]
 
 
-def check(dtype, got, want, what):
-    (assert_close_f32 if dtype == "float32" else assert_close_bf16)(got, want, what)
+def close_bf16(got, want, what):
+    """Rows within the bfloat16 tolerance of the other tests; of many rows, one in fifty (or one) may reach twice
+    that: a routed layer's weights are scores of a softmax, and a row in which two of them are close amplifies
+    the rounding of its input."""
+    from helpers import BF16_KL_TOL, BF16_LOGIT_TOL, kl_rows
+    got, want = np.asarray(got, dtype=np.float64), np.asarray(want, dtype=np.float64)
+    assert got.shape == want.shape and np.isfinite(got).all(), what
+    err = np.max(np.abs(got - want), axis=-1) / (np.max(np.abs(want), axis=-1) + 1e-30)
+    over = int((err > BF16_LOGIT_TOL).sum())
+    assert err.max() <= 2 * BF16_LOGIT_TOL and over <= max(1, len(err) // 50), \
+        f"{what}: worst logit error {err.max():.3e}, {over} of {len(err)} rows over {BF16_LOGIT_TOL}"
+    kl = kl_rows(want, got)
+    assert kl.max() <= 2 * BF16_KL_TOL and int((kl > BF16_KL_TOL).sum()) <= max(1, len(err) // 50), f"{what}: worst KL {kl.max():.3e}"
 
 
-def same_cut(dtype, got, base, what):
-    got, base = np.asarray(got), np.asarray(base)
+class Run:
+    """Logits of one sequence and what its routers chose."""
+
+    def __init__(self, logits, forced):
+        self.logits, self.forced = logits, forced
+
+
+def check(dtype, cfg, t, ids, run, what, rows=None):
+    """A run against the plain implementation.  float32: the plain implementation chooses for itself.  bfloat16: it
+    follows the run's choices (they may differ where two are within bfloat16's rounding), and the choices
+    must agree with the plain ones wherever those are clear."""
+    rows = slice(None) if rows is None else rows
     if dtype == "float32":
-        assert np.array_equal(got, base), f"{what}: first difference at {first_difference(got, base)}"
+        assert_close_f32(run.logits[rows], H.plain_logits(cfg, t, ids)[rows], what)
+        return
+    close_bf16(run.logits[rows], H.plain_logits(cfg, t, ids, None, None, run.forced)[rows], what)
+    if run.forced:
+        overall, clear = H.agreement(cfg, t, ids, run.forced, clear=0.15)
+        assert clear >= 0.98 and overall >= 0.85, f"{what}: routers agree on {overall:.3f} of all rows, {clear:.3f} of the clear ones"
+
+
+def same_cut(dtype, cfg, t, ids, run, base, what):
+    """Two runs of one sequence cut differently: the same bits in float32; in bfloat16 each is held against the
+    plain implementation (a router may choose differently in the two)."""
+    if dtype == "float32":
+        got, want = np.asarray(run.logits), np.asarray(base.logits)
+        assert np.array_equal(got, want), f"{what}: first difference at {first_difference(got, want)}"
     else:
-        err = np.max(np.abs(got - base) / (np.max(np.abs(base), axis=-1, keepdims=True) + 1e-30))
-        assert err <= BF16_SELF_TOL, f"{what}: {err:.3e}"
+        check(dtype, cfg, t, ids, run, what)
 
 
 def ids_for(cfg, t, n, dtype, seed=0):
     return H.clear_ids(cfg, t, n, seed, MARGIN[dtype])
 
 
-def whole(eng, ids):
-    s = eng.new_sequence()
-    try:
-        return eng.step([s], [ids], [list(range(len(ids)))]).cpu().numpy()
-    finally:
-        eng.free_sequence(s)
-
-
 def in_pieces(eng, ids, cuts):
-    s = eng.new_sequence()
-    out, at = [], 0
-    try:
-        for c in list(cuts) + [len(ids)]:
-            piece = ids[at:at + c]
-            if not piece:
-                break
-            out.append(eng.step([s], [piece], [list(range(len(piece)))]).cpu().numpy())
-            at += len(piece)
-    finally:
-        eng.free_sequence(s)
-    return np.concatenate(out)
+    """The prompt cut at `cuts` (piece sizes, the last piece takes the rest): logits of all places, and the choices."""
+    with H.Choices(eng) as rec:
+        s = eng.new_sequence()
+        out, at = [], 0
+        try:
+            for c in list(cuts) + [len(ids)]:
+                piece = ids[at:at + c]
+                if not piece:
+                    break
+                out.append(eng.step([s], [piece], [list(range(len(piece)))]).cpu().numpy())
+                at += len(piece)
+            forced = rec.of(s, len(ids))
+        finally:
+            eng.free_sequence(s)
+    return Run(np.concatenate(out), forced)
+
+
+def whole(eng, ids):
+    return in_pieces(eng, ids, [])
 
 
 # ------------------------------------------------------------------------------------------ row-wise kernels
@@ -127,10 +161,10 @@ def test_whole_projection_norm_rotation_and_cache_write(dtype, H_, G, D, Dv, rot
     q_out = torch.empty((rows, H_ * D), dtype=dtype, device=DEV)
     view = cache.kv_view(0)
     ops.whole_norm_rope_kv_write(src, H_ * D, H_ * D + G * D, wq, wk, eps, freq, rot, None, q_out, H_, view, slots, pos, rows, True)
-    x = src.float().cpu()
+    x = src.double().cpu()
     p_cpu = pos.cpu()
-    q_want = P.rotate_half_layout(P.rms_norm(x[:, :H_ * D], wq.cpu(), eps).view(rows, H_, D), p_cpu, rot, base)
-    k_want = P.rotate_half_layout(P.rms_norm(x[:, H_ * D:H_ * D + G * D], wk.cpu(), eps).view(rows, G, D), p_cpu, rot, base)
+    q_want = P.rotate_half_layout(P.rms_norm(x[:, :H_ * D], wq.cpu().double(), eps).view(rows, H_, D), p_cpu, rot, base)
+    k_want = P.rotate_half_layout(P.rms_norm(x[:, H_ * D:H_ * D + G * D], wk.cpu().double(), eps).view(rows, G, D), p_cpu, rot, base)
     tol = 3e-6 if dtype == torch.float32 else 2 ** -8
     assert (q_out.float().cpu().view(rows, H_, D) - q_want).abs().max() <= tol * q_want.abs().max()
     # read the cache back through the plain attention kernel's view of it: one-hot queries would be roundabout,
@@ -143,13 +177,13 @@ def test_whole_projection_norm_rotation_and_cache_write(dtype, H_, G, D, Dv, rot
         keys = store[page, :G * 64 * D].view(G, 64, D)[:, at]
         vals = store[page, G * 64 * D:].view(G, 64, Dv)[:, at]
         assert (keys - k_want[r]).abs().max() <= tol * k_want.abs().max()
-        assert torch.equal(vals, x[r, H_ * D + G * D:].view(G, Dv))
+        assert torch.equal(vals.double(), x[r, H_ * D + G * D:].view(G, Dv))
 
 
 def plain_route(z, corr, groups, keep, top):
     cfg = {"experts": z.shape[1], "top": top, "groups": {"count": groups, "keep": keep}}
     w = {"r.router": torch.eye(z.shape[1]), "r.correction": corr}
-    return P.route(z, cfg, w, "r.")
+    return P.route(z.double(), cfg, w, "r.")
 
 
 @pytest.mark.parametrize("n,groups,keep,top", [(10, 2, 1, 2), (8, 1, 1, 3), (12, 4, 2, 5), (6, 3, 2, 1), (64, 8, 3, 6), (7, 7, 2, 2)])
@@ -295,7 +329,7 @@ def test_each_request_alone_and_whole(name, lengths, dtype):
     eng, cfg, t = engine(name, dtype)
     for k, n in enumerate(lengths):
         ids = ids_for(cfg, t, n, dtype, seed=k)
-        check(dtype, whole(eng, ids), H.plain_logits(cfg, t, ids), f"{name} len {n}")
+        check(dtype, cfg, t, ids, whole(eng, ids), f"{name} len {n}")
 
 
 def test_residual_stream_after_every_layer():
@@ -327,8 +361,9 @@ def test_soft_routing_in_float32():
     for name in ("mixed", "odd"):
         eng, cfg, t = engine(name, "float32", soft=True)
         ids = H.clear_ids(cfg, t, 120, 4, 1e-4)
-        check("float32", whole(eng, ids), H.plain_logits(cfg, t, ids), name)
-        same_cut("float32", in_pieces(eng, ids, [50, 3] + [1] * 67), whole(eng, ids), name)
+        base = whole(eng, ids)
+        check("float32", cfg, t, ids, base, name)
+        same_cut("float32", cfg, t, ids, in_pieces(eng, ids, [50, 3] + [1] * 67), base, name)
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
@@ -338,8 +373,8 @@ def test_prefill_against_token_by_token(name, n, tail, dtype):
     ids = ids_for(cfg, t, n, dtype, seed=5)
     base = whole(eng, ids)
     got = in_pieces(eng, ids, [n - tail] + [1] * tail)
-    same_cut(dtype, got, base, f"{name}: last {tail} one by one")
-    check(dtype, got, H.plain_logits(cfg, t, ids), f"{name} decoded")
+    same_cut(dtype, cfg, t, ids, got, base, f"{name}: last {tail} one by one")
+    check(dtype, cfg, t, ids, got, f"{name} decoded")
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
@@ -349,14 +384,14 @@ def test_prompt_in_portions_down_to_two_tokens(name, dtype):
     ids = ids_for(cfg, t, 170, dtype, seed=6)
     base = whole(eng, ids)
     for cuts in ([2] * 30, [64, 64], [63, 2, 1, 64], [37, 37, 37, 37], [3, 125, 2], [129]):
-        same_cut(dtype, in_pieces(eng, ids, cuts), base, f"{name} cut {cuts[:4]}")
-    check(dtype, base, H.plain_logits(cfg, t, ids), name)
+        same_cut(dtype, cfg, t, ids, in_pieces(eng, ids, cuts), base, f"{name} cut {cuts[:4]}")
+    check(dtype, cfg, t, ids, base, name)
 
 
 def test_a_step_cut_into_passes_inside_prompts():
     eng, cfg, t = engine("mixed", "float32", max_step_tokens=64)
     ids = ids_for(cfg, t, 150, "float32", seed=7)
-    assert np.array_equal(whole(eng, ids), whole(engine("mixed", "float32")[0], ids))
+    assert np.array_equal(whole(eng, ids).logits, whole(engine("mixed", "float32")[0], ids).logits)
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
@@ -368,26 +403,28 @@ def test_unequal_batches_against_each_alone_with_slots_used_again(name, dtype):
         full = [ids_for(cfg, t, n + steps[k], dtype, seed=10 * round_ + k) for k, n in enumerate(lengths)]
         prompts = [f[:n] for f, n in zip(full, lengths)]
         tails = [f[n:] for f, n in zip(full, lengths)]
-        slots = [eng.new_sequence() for _ in lengths]
-        got = [[] for _ in lengths]
-        first = eng.step(slots, prompts, [list(range(n)) for n in lengths]).cpu().numpy()
-        at = 0
-        for k, n in enumerate(lengths):
-            got[k].append(first[at:at + n])
-            at += n
-        live = list(range(len(lengths)))
-        for step in range(max(steps)):
-            live = [k for k in live if step < steps[k]]         # the shorter requests end earlier
-            out = eng.step([slots[k] for k in live], [[tails[k][step]] for k in live]).cpu().numpy()
-            for j, k in enumerate(live):
-                got[k].append(out[j:j + 1])
-        for s in slots:
-            eng.free_sequence(s)
+        with H.Choices(eng) as rec:
+            slots = [eng.new_sequence() for _ in lengths]
+            got = [[] for _ in lengths]
+            first = eng.step(slots, prompts, [list(range(n)) for n in lengths]).cpu().numpy()
+            at = 0
+            for k, n in enumerate(lengths):
+                got[k].append(first[at:at + n])
+                at += n
+            live = list(range(len(lengths)))
+            for step in range(max(steps)):
+                live = [k for k in live if step < steps[k]]         # the shorter requests end earlier
+                out = eng.step([slots[k] for k in live], [[tails[k][step]] for k in live]).cpu().numpy()
+                for j, k in enumerate(live):
+                    got[k].append(out[j:j + 1])
+            runs = [Run(np.concatenate(got[k]), rec.of(slots[k], len(full[k]))) for k in range(len(lengths))]
+            for s in slots:
+                eng.free_sequence(s)
         for k, n in enumerate(lengths):
             alone = whole(eng, full[k])
-            same_cut(dtype, np.concatenate(got[k]), alone, f"{name} round {round_} request {k}")
+            same_cut(dtype, cfg, t, full[k], runs[k], alone, f"{name} round {round_} request {k}")
             if round_ == 0:
-                check(dtype, alone, H.plain_logits(cfg, t, full[k]), f"{name} request {k}")
+                check(dtype, cfg, t, full[k], alone, f"{name} request {k}")
 
 
 # ------------------------------------------------------------------------------------------ edges, far keys
@@ -409,18 +446,17 @@ def test_window_edges_and_kept_keys_that_decide(dtype):
     many = 60 if dtype == "float32" else 25
     assert moved(lambda m: {**m, "size": m["size"] + 1}) > many
     assert moved(lambda m: {**m, "keep_first": max(m["keep_first"] - 1, 0)}) > many
-    check(dtype, whole(eng, ids), want, "prompt")
-    got = in_pieces(eng, ids, [30] + [1] * 230)
-    check(dtype, got, want, "decoded across window edges, kept keys and page borders")
+    check(dtype, cfg, t, ids, whole(eng, ids), "prompt")
+    check(dtype, cfg, t, ids, in_pieces(eng, ids, [30] + [1] * 230), "decoded across window edges, kept keys and page borders")
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
 def test_a_kept_key_far_back_and_the_sink(dtype):
     """The first token's key is made to dominate a late query: one key direction of head 0 is aligned with
-    that token's embedding and the same query direction with the last token's, so the late logits hang on a kept key hundreds of
-    positions back, outside every window, read in a prompt and in decoding.  The sinks are raised until they
-    hold a good part of the denominators.  Without the kept key, and without the sinks, the plain result
-    differs by more than the tolerance."""
+    that token's embedding and the same query direction with the last token's, so the late logits hang on a
+    kept key hundreds of positions back, outside every window, read in a prompt and in decoding.  The sinks
+    are raised until they hold a good part of the denominators.  Without the kept key, and without the
+    sinks, the plain result differs by more than the tolerance."""
     from x0ne_engine_b200 import Engine
     cfg = H.config([H.layer(H.attention(heads=4, kv_heads=2, window=30, keep=2, rot=None), None),
                     H.layer(H.attention(heads=4, kv_heads=2, window=45, keep=1, rot=None, kv_from=0), H.dense(64))])
@@ -452,25 +488,23 @@ def test_a_kept_key_far_back_and_the_sink(dtype):
         no_sink[k] = t[k] - 40.0
     assert np.abs(H.plain_logits(cfg, no_sink, ids)[-1] - want[-1]).max() > 0.06 * np.abs(want[-1]).max()
     eng = Engine.from_folder(d, dtype=dtype, max_tokens=1024, max_seq_len=1024)
-    check(dtype, whole(eng, ids)[-3:], want, "kept key in a prompt")
-    check(dtype, in_pieces(eng, ids, [697, 1, 1])[-3:], want, "kept key decoded")
+    check(dtype, cfg, t, ids, whole(eng, ids), "kept key in a prompt", rows=slice(-3, None))
+    check(dtype, cfg, t, ids, in_pieces(eng, ids, [697, 1, 1]), "kept key decoded", rows=slice(-3, None))
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
 def test_first_tokens_of_a_sequence(dtype):
     eng, cfg, t = engine("mixed", dtype)
     ids = ids_for(cfg, t, 6, dtype, seed=11)
-    want = H.plain_logits(cfg, t, ids)
-    check(dtype, in_pieces(eng, ids, [1, 1, 1, 1, 1]), want, "first tokens one by one")
-    check(dtype, in_pieces(eng, ids, [2, 2]), want, "first tokens in twos")
+    check(dtype, cfg, t, ids, in_pieces(eng, ids, [1, 1, 1, 1, 1]), "first tokens one by one")
+    check(dtype, cfg, t, ids, in_pieces(eng, ids, [2, 2]), "first tokens in twos")
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
 def test_long_decoding(dtype):
     eng, cfg, t = engine("even", dtype)
     ids = ids_for(cfg, t, 420, dtype, seed=12)
-    got = in_pieces(eng, ids, [20] + [1] * 400)
-    check(dtype, got, H.plain_logits(cfg, t, ids), "400 decoded tokens")
+    check(dtype, cfg, t, ids, in_pieces(eng, ids, [20] + [1] * 400), "400 decoded tokens")
 
 
 # ------------------------------------------------------------------------------------------ generation
@@ -490,7 +524,7 @@ def test_greedy_generation_through_the_entry_point(decode, dtype):
             margins = []
             row = H.plain_logits(cfg, t, ids, None, margins)[-1]
             top = np.sort(row)[-2:]
-            clear_route = min(float(x.min()) for x in margins) >= MARGIN[dtype]
+            clear_route = min(float(x.min()) for x in margins) >= (1e-4 if dtype == "float32" else 0.15)
             if tok != int(np.argmax(row)):
                 tol = 1e-4 if dtype == "float32" else 2 * 0.05
                 assert not clear_route or top[1] - top[0] <= tol * np.abs(row).max(), "a token left a clear argmax"
@@ -510,7 +544,7 @@ def test_random_model_from_a_configuration_generates():
 
 
 def test_short_prompt_passes_replayed_from_graphs_give_the_same_bits():
-    eng, cfg, t = engine("mixed", "bfloat16")
+    eng, cfg, t = engine("mixed", "bfloat16", pass_graphs=True)
     base, _, _ = engine("mixed", "bfloat16", pass_graphs=False)
     assert eng.replayable and eng.pass_graphs and not base.pass_graphs
     before = eng.pass_graph_replays
