@@ -13,9 +13,9 @@ time); `e2e` is the same rate through `Model.generate` with host token lists in 
 and 64 and the milliseconds a 128-token and a 512-token prompt take through the step function; `roofline` places the decode step against the bytes it must read.  One JSON line is
 printed.  This library runs on one GPU: for --gpus above 1 a line says so and the exit code is 2.
 
-    python bench.py --design rovurax [--sizes 1.7b,8b] [--layers 8] [--chunk 1024] [--steps K]
+    python bench.py --design rovurax|tenetar [--sizes 1.7b,8b] [--layers 8] [--chunk 1024] [--steps K]
 
-instead runs the Rovurax design beside Qwen3 at equal sizes (random bfloat16 weights, the same engine,
+instead runs that design beside Qwen3 at equal sizes (random bfloat16 weights, the same engine,
 step function and decode graphs): one prompt of --prefill-tokens through the step function, then decode
 at --batch, device-timed; one JSON line with a row per size and design.
 """
@@ -147,13 +147,38 @@ DESIGN_SIZES = {
 }
 
 
-def design_configs(size: dict, layers: int, vocab: int, chunk: int):
-    """(Rovurax configuration, Qwen3 configuration) with the same width, heads, feed-forward, depth and
+def tenetar_config(size: dict, layers: int, vocab: int, window: int):
+    """A Tenetar configuration of the given layer sizes.  Of every four layers the first two keep keys and values
+    and the other two read the second one's; the first layer of the model has a dense feed-forward of the full
+    width, the others 16 experts of a quarter of it plus 2 identity experts in 6 groups of 3 of which 3 stay,
+    4 chosen per token, and a gated shared expert of the same quarter: about the dense layer's work per token."""
+    from x0ne_engine_b200.config import config_from_dict
+    w, ff, H, G, d = size["width"], size["ff"], size["heads"], size["kv_heads"], size["dim"]
+    moe = {"kind": "moe", "expert": {"ff": ff // 4}, "shared": {"ff": ff // 4},
+           "router": {"experts": 16, "identity": 2, "top": 4, "groups": {"count": 6, "keep": 3}}}
+    out = []
+    for i in range(layers):
+        mixer = {"dim": d, "heads": H, "kv_heads": G, "vdim": d, "scale": d ** -0.5, "mask": {"size": window, "keep_first": 4},
+                 "rot": {"base": 1000000.0, "dims": d}}
+        if i % 4 >= 2:
+            mixer["kv_from"] = i - i % 4 + 1
+        out.append({"type": "attention", "mixer": mixer, "mlp": {"kind": "dense", "ff": ff} if i == 0 else moe})
+    return config_from_dict({"architecture": "Tenetar", "vocab": vocab, "width": w, "norm": {"eps": 1e-6},
+                             "embedding": {"scale": float(w) ** 0.5}, "layers": out})
+
+
+def design_configs(size: dict, layers: int, vocab: int, chunk: int, design: str = "rovurax"):
+    """(the design's configuration, Qwen3 configuration) with the same width, heads, feed-forward, depth and
     vocabulary.  Of every four Rovurax layers three are chunk-masked attention with blended values and
-    one is latent attention with YaRN-scaled rotation, a sink and a gate."""
+    one is latent attention with YaRN-scaled rotation, a sink and a gate; Tenetar: see tenetar_config."""
     import x0ne_engine_b200 as x
     from x0ne_engine_b200.config import config_from_dict
     w, ff, H, G, d = size["width"], size["ff"], size["heads"], size["kv_heads"], size["dim"]
+    old = x.Qwen3Config(hidden_size=w, intermediate_size=ff, num_hidden_layers=layers, num_attention_heads=H,
+                        num_key_value_heads=G, head_dim=d, vocab_size=vocab, max_position_embeddings=40960,
+                        rms_norm_eps=1e-6, rope_theta=1000000.0, tie_word_embeddings=False, dtype="bfloat16")
+    if design == "tenetar":
+        return tenetar_config(size, layers, vocab, chunk), old
     mlp = {"ff": ff, "kind": "dense", "limit": 7.0}
     att = {"type": "attention", "mlp": mlp, "mixer": {"dim": d, "heads": H, "kv_heads": G, "vdim": d, "scale": d ** -0.5,
                                                         "mask": {"size": chunk}, "v_mix": True}}
@@ -162,9 +187,6 @@ def design_configs(size: dict, layers: int, vocab: int, chunk: int):
         "rot": {"base": 1000000.0, "dims": size["rot_dim"], "scaling": {"factor": 4.0, "original": 4096, "fast": 32.0, "slow": 1.0}}}}
     new = config_from_dict({"architecture": "Rovurax", "vocab": vocab, "width": w, "norm": {"eps": 1e-6},
                             "layers": [lat if i % 4 == 3 else att for i in range(layers)]})
-    old = x.Qwen3Config(hidden_size=w, intermediate_size=ff, num_hidden_layers=layers, num_attention_heads=H,
-                        num_key_value_heads=G, head_dim=d, vocab_size=vocab, max_position_embeddings=40960,
-                        rms_norm_eps=1e-6, rope_theta=1000000.0, tie_word_embeddings=False, dtype="bfloat16")
     return new, old
 
 
@@ -185,7 +207,7 @@ def design_bench(args) -> int:
     rows_out = []
     for name in args.sizes.split(","):
         size = DESIGN_SIZES[name]
-        for design, cfg in zip(("rovurax", "qwen3"), design_configs(size, layers, vocab, args.chunk)):
+        for design, cfg in zip((args.design, "qwen3"), design_configs(size, layers, vocab, args.chunk, args.design)):
             model = x.Model.random(cfg, seed=0, dtype="bfloat16", max_batch=B, max_ctx=ctx, max_step_tokens=max(T, 64))
             eng = model.engine
             ids = synthetic_ids(T, vocab, 20261104)
@@ -235,7 +257,7 @@ def design_bench(args) -> int:
                   f"({rows_out[-1]['decode_frac_of_hbm']:.2f} of {pk['source']} copy bandwidth)", file=sys.stderr, flush=True)
             del runner, model, eng
             torch.cuda.empty_cache()
-    print(json.dumps({"metric": "prefill and decode tokens/s of Rovurax beside Qwen3 at equal sizes (random bf16 weights)",
+    print(json.dumps({"metric": f"prefill and decode tokens/s of {args.design.capitalize()} beside Qwen3 at equal sizes (random bf16 weights)",
                       "unit": "tokens/s", "n_gpus": 1, "steps": K, "warmup": W, "dtype": "bf16", "data": "synthetic",
                       "impl": "ours", "chunk": args.chunk, "peaks": pk, "rows": rows_out}))
     return 0
@@ -253,10 +275,11 @@ def main() -> int:
     ap.add_argument("--prefill-tokens", type=int, default=2048)
     ap.add_argument("--no-points", action="store_true", help="skip decode at batch 1 and 64")
     ap.add_argument("--no-e2e", action="store_true")
-    ap.add_argument("--design", default=None, choices=["rovurax"],
+    ap.add_argument("--design", default=None, choices=["rovurax", "tenetar"],
                     help="instead of the default workload: this design beside Qwen3 at equal sizes (prefill and decode)")
     ap.add_argument("--sizes", default="1.7b,8b", help="with --design: which of " + ", ".join(DESIGN_SIZES))
-    ap.add_argument("--chunk", type=int, default=1024, help="with --design: positions per chunk of the masked attention")
+    ap.add_argument("--chunk", type=int, default=1024,
+                    help="with --design: positions per chunk of the masked attention (rovurax) or of the sliding window (tenetar)")
     args = ap.parse_args()
     if args.design is not None and args.impl == "ours" and args.gpus == 1:
         return design_bench(args)

@@ -591,7 +591,7 @@ def test_toy_arrangements_embedding_and_head_are_registered_from_here():
     class ScaledEmbedding(TokenEmbedding):
         def forward(self, ctx, resid, n_rows):
             super().forward(ctx, resid, n_rows)
-            resid[:n_rows] *= float(self.spec["scale"])
+            resid[:n_rows] *= float(self.spec["boost"])        # (a parameter of its own: "scale" is the library embedding's)
 
     class CappedHead(LMHead):
         def forward(self, normed, logits, n_rows):
@@ -614,7 +614,7 @@ def test_toy_arrangements_embedding_and_head_are_registered_from_here():
         layers = (LayerSpec("toy_parallel", dict(norm=norm("l0.n"), mixer=att(0), ffn=ffn)),
                   LayerSpec("toy_mixer_only", dict(norm=norm("l1.n"), mixer=att(1))))
         spec = ModelSpec(architecture="ToyForCausalLM", vocab_size=vocab, hidden_size=h, max_position_embeddings=128,
-                         embedding=PartSpec("toy_scaled_embedding", dict(vocab_size=vocab, hidden_size=h, scale=scale,
+                         embedding=PartSpec("toy_scaled_embedding", dict(vocab_size=vocab, hidden_size=h, boost=scale,
                                                                          names=dict(weight="emb"))),
                          positions={"rope": PartSpec("rope", dict(head_dim=hd, rotary_dim=hd, theta=theta))},
                          layers=layers, run_order=(RunEntry(0), RunEntry(1)), final_norm=norm("fn"),

@@ -245,6 +245,53 @@ def test_experts_over_grouped_pairs(dtype, rows, E, I, top, hidden, ff):
     assert (out.double().cpu() - want).abs().max() <= tol * want.abs().max()
 
 
+@pytest.mark.parametrize("rows,E,I,top,hidden,ff", [(100, 5, 1, 3, 72, 40), (700, 16, 2, 4, 256, 192), (513, 3, 0, 1, 320, 600)])
+def test_experts_on_the_tensor_cores(rows, E, I, top, hidden, ff):
+    """Tiles of 128 listed pairs on tcgen05 (rows gathered into the listed order, activations kept in it, the down
+    product written by pair) against a loop over rows and choices; widths that end inside a tile of 256 outputs
+    and inside a slice of 64 inner values, experts with no pair and with more than a tile of them."""
+    from x0ne_engine_b200.csrc import ops
+    g = torch.Generator().manual_seed(rows)
+    dtype = torch.bfloat16
+    x = torch.randn(rows, hidden, generator=g).to(dtype)
+    up = (torch.randn(E, ff, hidden, generator=g) / hidden ** 0.5).to(dtype)
+    down = (torch.randn(E, hidden, ff, generator=g) / ff ** 0.5).to(dtype)
+    n_out = E + I
+    prefer = torch.rand(n_out, generator=g) ** 3                 # unequal loads; the last real expert gets no pair at all
+    prefer[E - 1] = 0
+    chosen = torch.stack([torch.multinomial(prefer + 1e-9 * (torch.arange(n_out) != E - 1), top, generator=g) for _ in range(rows)]).to(torch.int32)
+    weights = torch.rand(rows, top, generator=g)
+    pairs = rows * top
+    assert ops.moe_tc_takes(dtype, pairs, hidden, ff)
+    n_tiles = ops.moe_max_tiles(pairs, E, ops.MOE_TC_TILE_ROWS)
+    i32 = lambda *shape: torch.empty(shape, dtype=torch.int32, device=DEV)
+    offsets, listed, tiles, n_real = i32(E + 1), i32(pairs), i32(n_tiles, 3), i32(1)
+    xs = torch.full((pairs, hidden), float("nan"), dtype=dtype, device=DEV)      # places that hold no pair keep whatever was there
+    act = torch.empty((pairs, ff), dtype=dtype, device=DEV)
+    y = torch.empty((pairs, hidden), dtype=torch.float32, device=DEV)
+    out = torch.empty((rows, hidden), dtype=dtype, device=DEV)
+    xd, ch = x.to(DEV), chosen.to(DEV)
+    ops.moe_group(ch, pairs, E, offsets, listed, tiles, ops.MOE_TC_TILE_ROWS, n_real)
+    counts = [int((chosen.flatten() == e).sum()) for e in range(E)]
+    assert int(n_real[0]) == sum(-(-c // 128) for c in counts) and counts[E - 1] == 0 and (max(counts) > 128 or rows < 200)
+    ops.moe_gather_rows(xd, listed, offsets, E, top, xs, pairs)
+    ops.moe_product_tc(0, xs, up.to(DEV), listed, tiles, n_real, n_tiles, act)
+    ops.moe_product_tc(1, act, down.to(DEV), listed, tiles, n_real, n_tiles, y)
+    ops.check_tc_status(torch.device(DEV))
+    ops.moe_combine(y, xd, ch, weights.to(DEV), top, E, None, None, out, rows)
+    want = torch.zeros(rows, hidden, dtype=torch.float64)
+    for r in range(rows):
+        for j in range(top):
+            e = int(chosen[r, j])
+            if e >= E:
+                v = x[r].double()
+            else:
+                a = torch.relu(up[e].double() @ x[r].double()).square().to(dtype).double()      # the activations are kept in bfloat16
+                v = a @ down[e].double().T
+            want[r] += weights[r, j].double() * v
+    assert (out.double().cpu() - want).abs().max() <= 2 ** -7 * want.abs().max()
+
+
 ATT_CASES = [  # q_heads, kv_heads, dk, dv, window, keep_first, sink
     (4, 2, 48, None, 100, 4, True),
     (6, 2, 20, 12, 37, 70, True),        # kept keys on two pages

@@ -109,10 +109,12 @@ __global__ void moe_route_kernel(const float* __restrict__ z, int ldz, const flo
 // Grouping: pairs listed expert by expert, and the table of tiles.  One block.
 //   offsets [experts + 1]   first place of each expert in `listed`
 //   listed  [pairs]         pair numbers, expert by expert (identity choices are in no list)
-//   tiles   [max_tiles][3]  expert, first place, count (count 0: the tile does not exist)
+//   tiles   [max_tiles][3]  expert, first place, count (count 0: the tile does not exist); tiles of tile_m pairs
+//   n_tiles_out             how many tiles exist (optional)
 // ----------------------------------------------------------------------------------------
 __global__ void moe_group_kernel(const int32_t* __restrict__ chosen, int pairs, int experts, int32_t* __restrict__ offsets,
-                                 int32_t* __restrict__ listed, int32_t* __restrict__ tiles, int max_tiles) {
+                                 int32_t* __restrict__ listed, int32_t* __restrict__ tiles, int max_tiles, int tile_m,
+                                 int32_t* __restrict__ n_tiles_out) {
     extern __shared__ int gp_smem[];
     int* count = gp_smem;                 // [experts]
     int* start = count + experts;         // [experts + 1]
@@ -131,7 +133,7 @@ __global__ void moe_group_kernel(const int32_t* __restrict__ chosen, int pairs, 
             start[e] = at;
             tile0[e] = t;
             at += count[e];
-            t += (count[e] + MOE_TILE_M - 1) / MOE_TILE_M;
+            t += (count[e] + tile_m - 1) / tile_m;
         }
         start[experts] = at;
         tile0[experts] = t;
@@ -140,13 +142,14 @@ __global__ void moe_group_kernel(const int32_t* __restrict__ chosen, int pairs, 
     for (int e = threadIdx.x; e <= experts; e += blockDim.x) offsets[e] = start[e];
     for (int e = threadIdx.x; e < experts; e += blockDim.x) {
         const int n = count[e];
-        for (int i = 0, t = tile0[e]; i < n && t < max_tiles; i += MOE_TILE_M, ++t) {
+        for (int i = 0, t = tile0[e]; i < n && t < max_tiles; i += tile_m, ++t) {
             tiles[3 * t] = e;
             tiles[3 * t + 1] = start[e] + i;
-            tiles[3 * t + 2] = min(MOE_TILE_M, n - i);
+            tiles[3 * t + 2] = min(tile_m, n - i);
         }
     }
     for (int t = tile0[experts] + threadIdx.x; t < max_tiles; t += blockDim.x) tiles[3 * t + 2] = 0;
+    if (threadIdx.x == 0 && n_tiles_out != nullptr) n_tiles_out[0] = min(tile0[experts], max_tiles);
     __syncthreads();
     for (int e = threadIdx.x; e < experts; e += blockDim.x) count[e] = 0;
     __syncthreads();
@@ -259,9 +262,9 @@ __global__ void moe_combine_kernel(const float* __restrict__ y, const T* __restr
 // ----------------------------------------------------------------------------------------
 X0NE_API int x0ne_moe_tile_rows() { return MOE_TILE_M; }
 
-// Tiles a pass of `pairs` pairs over `experts` experts can need at most.
-X0NE_API int x0ne_moe_max_tiles(int pairs, int experts) {
-    const int full = pairs / MOE_TILE_M + experts;          // every expert may end in a partial tile
+// Tiles of tile_m pairs a pass of `pairs` pairs over `experts` experts can need at most.
+X0NE_API int x0ne_moe_max_tiles(int pairs, int experts, int tile_m) {
+    const int full = pairs / tile_m + experts;              // every expert may end in a partial tile
     return full < pairs ? full : (pairs > 0 ? pairs : 1);   // (never more tiles than pairs)
 }
 
@@ -281,13 +284,14 @@ X0NE_API int x0ne_moe_route(const float* z, int ldz, const float* correction, in
 }
 
 X0NE_API int x0ne_moe_group(const int32_t* chosen, int pairs, int experts, int32_t* offsets, int32_t* listed, int32_t* tiles,
-                            int max_tiles, cudaStream_t stream) {
-    X0NE_REQUIRE(pairs >= 0 && experts > 0 && max_tiles >= x0ne_moe_max_tiles(pairs, experts), "moe_group: pairs %d experts %d tiles %d",
-                 pairs, experts, max_tiles);
+                            int max_tiles, int tile_m, int32_t* n_tiles_out, cudaStream_t stream) {
+    X0NE_REQUIRE(pairs >= 0 && experts > 0 && tile_m > 0 && max_tiles >= x0ne_moe_max_tiles(pairs, experts, tile_m),
+                 "moe_group: pairs %d experts %d tiles %d of %d", pairs, experts, max_tiles, tile_m);
     if (pairs == 0) return 0;
     const size_t smem = (size_t)(3 * experts + 2) * sizeof(int);
     X0NE_REQUIRE(smem <= 48 * 1024, "moe_group: %d experts are more than the kernel holds", experts);
-    x0ne_launch(moe_group_kernel, dim3(1), dim3(1024), smem, stream, chosen, pairs, experts, offsets, listed, tiles, max_tiles);
+    x0ne_launch(moe_group_kernel, dim3(1), dim3(1024), smem, stream, chosen, pairs, experts, offsets, listed, tiles, max_tiles, tile_m,
+                n_tiles_out);
     X0NE_LAUNCH_CHECK();
 }
 

@@ -79,7 +79,9 @@ _SIGNATURES = {
     "x0ne_whole_norm_rope_kv_write": [_P, _I, _I, _I, _I, _P, _P, _F, _P, _I, _P, _I, _P, _I, None, _P, _P, _I, _I, _P],
     "x0ne_relu2": [_P, _P, _I, _L, _P],
     "x0ne_moe_route": [_P, _I, _P, _I, _I, _I, _I, _I, _P, _P, _P, _I, _P],
-    "x0ne_moe_group": [_P, _I, _I, _P, _P, _P, _I, _P],
+    "x0ne_moe_group": [_P, _I, _I, _P, _P, _P, _I, _I, _P, _P],
+    "x0ne_moe_gather_rows": [_P, _I, _P, _P, _I, _I, _P, _I, _P],
+    "x0ne_moe_product_tc": [_I, _P, _L, _P, _I, _I, _I, _P, _P, _P, _I, _P, _P, _P],
     "x0ne_moe_product": [_I, _P, _L, _P, _I, _I, _I, _P, _P, _I, _I, _P, _P],
     "x0ne_moe_combine": [_P, _P, _I, _P, _P, _I, _I, _P, _P, _P, _I, _I, _P],
     "x0ne_add_rmsnorm": [_P, _P, _P, _P, _I, _P, _I, _I, _F, _P],
@@ -312,13 +314,21 @@ def relu2(x: torch.Tensor, out: torch.Tensor, n_rows: int) -> None:
 # ---------------------------------------------------------------------------------------------
 # routed feed-forward (csrc/moe.cu, module `core`; the tensor-core products in module `flex`)
 # ---------------------------------------------------------------------------------------------
-MOE_TILE_ROWS = 32       # pairs per tile of the grouped products (moe.cu: MOE_TILE_M)
+MOE_TILE_ROWS = 32       # pairs per tile of the grouped products on the CUDA cores (moe.cu: MOE_TILE_M)
+MOE_TC_TILE_ROWS = 128   # and on the tensor cores (moe_tcgen05.cu: MT_BM)
+MOE_TC_MIN_PAIRS = 256   # passes with at least this many (row, choice) pairs take the tensor-core kernel
 
 
-def moe_max_tiles(pairs: int, experts: int) -> int:
-    """Tiles a pass of `pairs` (row, choice) pairs over `experts` experts can need at most."""
-    full = pairs // MOE_TILE_ROWS + experts
+def moe_max_tiles(pairs: int, experts: int, tile_rows: int = MOE_TILE_ROWS) -> int:
+    """Tiles of `tile_rows` pairs a pass of `pairs` (row, choice) pairs over `experts` experts can need at most."""
+    full = pairs // tile_rows + experts
     return full if full < pairs else max(pairs, 1)
+
+
+def moe_tc_takes(dtype: torch.dtype, pairs: int, *widths: int) -> bool:
+    """Whether a pass's expert products go to the tensor-core kernel: bfloat16, enough pairs to fill its tiles,
+    and every inner width a multiple of 8 (a TMA row of whole 16-byte pieces)."""
+    return dtype == torch.bfloat16 and pairs >= MOE_TC_MIN_PAIRS and all(w % 8 == 0 for w in widths)
 
 
 def moe_route(z: torch.Tensor, correction: torch.Tensor, n: int, groups: int, keep: int, top: int, n_rows: int,
@@ -340,15 +350,47 @@ def moe_route(z: torch.Tensor, correction: torch.Tensor, n: int, groups: int, ke
 
 
 def moe_group(chosen: torch.Tensor, pairs: int, experts: int, offsets: torch.Tensor, listed: torch.Tensor,
-              tiles: torch.Tensor) -> None:
-    """Lists the pairs expert by expert and fills the table of tiles [max_tiles, 3] (expert, first place, count)."""
+              tiles: torch.Tensor, tile_rows: int = MOE_TILE_ROWS, n_tiles_out: Optional[torch.Tensor] = None) -> None:
+    """Lists the pairs expert by expert and fills the table of tiles [max_tiles, 3] (expert, first place, count) for
+    tiles of `tile_rows` pairs; `n_tiles_out` (one int32) receives how many tiles exist."""
     lib = _lib("core")
     for t, what in ((chosen, "chosen experts"), (offsets, "expert offsets"), (listed, "listed pairs"), (tiles, "tile table")):
         _need(t, torch.int32, what)
     if chosen.numel() < pairs or listed.numel() < pairs or offsets.numel() < experts + 1:
         raise KernelError("moe_group: buffers smaller than the pairs or experts asked for")
+    if n_tiles_out is not None:
+        _need(n_tiles_out, torch.int32, "tile count")
     _check(lib, lib.x0ne_moe_group(_ptr(chosen), pairs, experts, _ptr(offsets), _ptr(listed), _ptr(tiles), tiles.numel() // 3,
-                                   _stream()), "moe_group")
+                                   tile_rows, _ptr(n_tiles_out), _stream()), "moe_group")
+
+
+def moe_gather_rows(x: torch.Tensor, listed: torch.Tensor, offsets: torch.Tensor, experts: int, top: int, xs: torch.Tensor,
+                    pairs: int) -> None:
+    """xs[place] = x[listed[place] // top] for every place that holds a pair (bfloat16)."""
+    lib = _lib("tc")
+    _need(x, torch.bfloat16, "rows")
+    _need(xs, torch.bfloat16, "gathered rows")
+    if xs.shape[-1] != x.shape[-1] or xs.numel() < pairs * x.shape[-1]:
+        raise KernelError("moe_gather_rows: the gathered rows do not match")
+    _check(lib, lib.x0ne_moe_gather_rows(_ptr(x), x.shape[-1], _ptr(listed), _ptr(offsets), experts, top, _ptr(xs), pairs,
+                                         _stream()), "moe_gather_rows")
+
+
+def moe_product_tc(which: int, a: torch.Tensor, w: torch.Tensor, listed: torch.Tensor, tiles: torch.Tensor,
+                   n_real: torch.Tensor, max_tiles: int, out: torch.Tensor) -> None:
+    """The experts' products on tcgen05 over tiles of 128 listed pairs (moe_tcgen05.cu).  which 0: a = the gathered rows
+    [places, K], out = relu(.)^2 as bfloat16 [places, N]; which 1: a = those activations, out = float32 [pairs, N] by pair."""
+    global tc_used
+    lib = _lib("tc")
+    _need(a, torch.bfloat16, "expert input")
+    _need(w, torch.bfloat16, "expert weights")
+    _need(out, torch.float32 if which == 1 else torch.bfloat16, "expert output")
+    if w.dim() != 3 or a.shape[-1] != w.shape[2] or out.shape[-1] != w.shape[1] or tiles.numel() < 3 * max_tiles:
+        raise KernelError("moe_product_tc: shapes do not match")
+    tc_used = True
+    _check(lib, lib.x0ne_moe_product_tc(which, _ptr(a), a.numel() // a.shape[-1], _ptr(w), w.shape[0], w.shape[1], w.shape[2],
+                                        _ptr(listed), _ptr(tiles), _ptr(n_real), max_tiles, _ptr(out),
+                                        _ptr(gemm_tc_status(a.device)), _stream()), "moe_product_tc")
 
 
 def moe_product(which: int, a: torch.Tensor, w: torch.Tensor, listed: torch.Tensor, tiles: torch.Tensor, n_tiles: int, top: int,
@@ -363,22 +405,9 @@ def moe_product(which: int, a: torch.Tensor, w: torch.Tensor, listed: torch.Tens
     if w.dim() != 3 or a.shape[-1] != w.shape[2] or out.shape[-1] != w.shape[1] or tiles.numel() < 3 * n_tiles:
         raise KernelError("moe_product: shapes do not match")
     n, k = w.shape[1], w.shape[2]
-    if w.dtype == torch.bfloat16 and moe_tc_takes(n, k):
-        lib = _lib("flex")
-        _check(lib, lib.x0ne_moe_product_bf16(which, _ptr(a), a.shape[-1], _ptr(w), n, k, _ptr(listed), _ptr(tiles), n_tiles,
-                                              top, _ptr(out), _stream()), "moe_product_bf16")
-        return
     lib = _lib("core")
     _check(lib, lib.x0ne_moe_product(which, _ptr(a), a.shape[-1], _ptr(w), dtype_tag(w.dtype), n, k, _ptr(listed), _ptr(tiles),
                                      n_tiles, top, _ptr(out), _stream()), "moe_product")
-
-
-def moe_tc_takes(n: int, k: int) -> bool:
-    """Whether the tensor-core kernel of the experts' products takes weights [n, k]."""
-    return MOE_TC and n % 8 == 0 and k % 16 == 0
-
-
-MOE_TC = False
 
 
 def moe_combine(y: torch.Tensor, x: torch.Tensor, chosen: torch.Tensor, weights: torch.Tensor, top: int, experts: int,

@@ -84,9 +84,9 @@ class RoutedExperts(FeedForward):
             self.shared_down = Linear(tensors[n["shared_down"]])
 
     def weight_bytes(self) -> int:
-        """A step reads the router, the shared expert, and at most `top` experts per row; counted here for one row."""
-        per_expert = (self.up[0].numel() + self.down[0].numel()) * self.up.element_size()
-        total = self.router.weight_bytes() + min(self.top, self.experts) * per_expert
+        """The router, the shared expert and every expert: what a step of a batch large enough to reach all experts
+        reads (a small batch reads at most rows x top of them)."""
+        total = self.router.weight_bytes() + (self.up.numel() + self.down.numel()) * self.up.element_size()
         if self.shared_size:
             total += self.shared_up.weight_bytes() + self.shared_down.weight_bytes()
         return total
@@ -101,16 +101,27 @@ class RoutedExperts(FeedForward):
         offsets = ws.buffer("moe.offsets", (self.experts + 1,), torch.int32)
         listed = ws.buffer("moe.listed", (rows * top,), torch.int32)
         tiles = ws.buffer("moe.tiles", (ops.moe_max_tiles(rows * top, self.experts), 3), torch.int32)
+        n_real = ws.buffer("moe.n_tiles", (1,), torch.int32)
         act = ws.buffer("moe.act", (rows * top, self.inter), dt)
         y = ws.buffer("moe.y", (rows * top, self.hidden), torch.float32)
         out = ws.buffer(self.out_buffer, (rows, self.hidden), dt)
         self.router(x, z, n_rows)
         ops.moe_route(z, self.correction, self.n_out, self.groups, self.keep_groups, top, n_rows, chosen, weights, sgate, self.n_out)
         pairs = n_rows * top
-        n_tiles = ops.moe_max_tiles(pairs, self.experts)
-        ops.moe_group(chosen, pairs, self.experts, offsets, listed, tiles[:n_tiles])
-        ops.moe_product(0, x, self.up, listed, tiles, n_tiles, top, act)
-        ops.moe_product(1, act, self.down, listed, tiles, n_tiles, top, y)
+        if ops.moe_tc_takes(dt, pairs, self.hidden, self.inter):
+            # many pairs: tiles of 128 listed pairs on the tensor cores; the rows are gathered into the listed order first,
+            # the activations stay in that order, the down product writes by pair
+            n_tiles = ops.moe_max_tiles(pairs, self.experts, ops.MOE_TC_TILE_ROWS)
+            xs = ws.buffer("moe.gathered", (rows * top, self.hidden), dt)
+            ops.moe_group(chosen, pairs, self.experts, offsets, listed, tiles[:n_tiles], ops.MOE_TC_TILE_ROWS, n_real)
+            ops.moe_gather_rows(x, listed, offsets, self.experts, top, xs, pairs)
+            ops.moe_product_tc(0, xs, self.up, listed, tiles, n_real, n_tiles, act)
+            ops.moe_product_tc(1, act, self.down, listed, tiles, n_real, n_tiles, y)
+        else:
+            n_tiles = ops.moe_max_tiles(pairs, self.experts)
+            ops.moe_group(chosen, pairs, self.experts, offsets, listed, tiles[:n_tiles])
+            ops.moe_product(0, x, self.up, listed, tiles, n_tiles, top, act)
+            ops.moe_product(1, act, self.down, listed, tiles, n_tiles, top, y)
         shared = None
         if self.shared_size:
             su = ws.buffer("moe.shared_up", (rows, self.shared_size), dt)
