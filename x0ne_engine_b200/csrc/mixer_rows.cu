@@ -378,6 +378,92 @@ __global__ void whole_norm_rope_kv_write_kernel(const T* __restrict__ src, int l
     for (int i = threadIdx.x; i < G * vd; i += blockDim.x) base[v0 + (i / vd) * head_v + (i % vd)] = s[v_col + i];
 }
 
+// The same with 16-byte accesses: every width, column and half of the rotated part a multiple of 8.  A thread takes
+// pieces of 8 consecutive values; a rotated piece reads its partner piece (8 values rot/2 further on or back).
+template <typename T>
+__device__ __forceinline__ void wn_rotated_piece(const T* __restrict__ s, const float* __restrict__ w, int i, int D, int rot, int half,
+                                                 float scale, const float* __restrict__ cs, float* a) {
+    float wa[8];
+    load8f(s + i, a);
+    load8f(w + i, wa);
+    const int d = i % D;
+#pragma unroll
+    for (int k = 0; k < 8; ++k) a[k] = a[k] * scale * wa[k];
+    if (d < rot) {
+        const bool lo = d < half;
+        const int ip = lo ? i + half : i - half, j = lo ? d : d - half;
+        float b[8], wb[8];
+        load8f(s + ip, b);
+        load8f(w + ip, wb);
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+            const float bk = b[k] * scale * wb[k];
+            a[k] = lo ? a[k] * cs[j + k] - bk * cs[half + j + k] : a[k] * cs[j + k] + bk * cs[half + j + k];
+        }
+    }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256) whole_norm_rope_kv_write_vec_kernel(
+    const T* __restrict__ src, int ld, int k_col, int v_col, const float* __restrict__ norm_q, const float* __restrict__ norm_k,
+    float eps, const float* __restrict__ freq, int rot, const float* __restrict__ table, int table_positions, T* __restrict__ q_out,
+    int q_heads, PagedCache cache, const int32_t* __restrict__ row_slot, const int32_t* __restrict__ row_pos, int write_kv) {
+    extern __shared__ float cs[];
+    __shared__ float partial[32];
+    pdl_launch_dependents();
+    const int row = blockIdx.x;
+    const int slot = row_slot[row], pos = row_pos[row];
+    const int half = rot / 2;
+    for (int i = threadIdx.x; i < half; i += blockDim.x) {
+        if (pos >= 0 && pos < table_positions) {
+            cs[i] = table[(int64_t)pos * rot + i];
+            cs[half + i] = table[(int64_t)pos * rot + half + i];
+        } else {
+            float sn, c;
+            sincosf((float)pos * freq[i], &sn, &c);
+            cs[i] = c;
+            cs[half + i] = sn;
+        }
+    }
+    const int D = cache.head_dim, G = cache.kv_heads, vd = cache_v_dim(cache);
+    const int qn = q_heads * D, kn = write_kv ? G * D : 0, vn = write_kv ? G * vd : 0;
+    const int64_t k0 = write_kv ? cache_row_offset(cache, slot, pos, 0, 0) : -1;       // (page numbers are older than any running kernel)
+    const int64_t v0 = write_kv ? cache_row_offset(cache, slot, pos, 0, 1) : -1;
+    pdl_wait();
+    const T* s = src + (int64_t)row * ld;
+    float sq = 0.f, sk = 0.f;
+    for (int c = threadIdx.x; c < (qn + kn) / 8; c += blockDim.x) {
+        const int i = c * 8;
+        float v[8];
+        load8f(i < qn ? s + i : s + k_col + (i - qn), v);
+        float ss = 0.f;
+#pragma unroll
+        for (int k = 0; k < 8; ++k) ss = fmaf(v[k], v[k], ss);
+        if (i < qn) sq += ss; else sk += ss;
+    }
+    const float scale_q = 1.0f / sqrtf(block_reduce(sq, partial, OpSum(), 0.f) / (float)qn + eps);   // (syncs: cs is complete)
+    const float scale_k = write_kv ? 1.0f / sqrtf(block_reduce(sk, partial, OpSum(), 0.f) / (float)kn + eps) : 0.f;
+    T* qo = q_out + (int64_t)row * qn;
+    T* base = (T*)cache.base;
+    const int64_t head_k = (int64_t)cache.page_size * D, head_v = (int64_t)cache.page_size * vd;
+    for (int c = threadIdx.x; c < (qn + kn + vn) / 8; c += blockDim.x) {
+        const int i = c * 8;
+        float a[8];
+        if (i < qn) {
+            wn_rotated_piece(s, norm_q, i, D, rot, half, scale_q, cs, a);
+            store8f(qo + i, a);
+        } else if (i < qn + kn) {
+            const int ik = i - qn;
+            if (k0 < 0) continue;
+            wn_rotated_piece(s + k_col, norm_k, ik, D, rot, half, scale_k, cs, a);
+            store8f(base + k0 + (ik / D) * head_k + ik % D, a);
+        } else {
+            const int iv = i - qn - kn;
+            if (v0 >= 0) copy8(base + v0 + (iv / vd) * head_v + iv % vd, s + v_col + iv);
+        }
+    }
+}
+
 X0NE_API int x0ne_whole_norm_rope_kv_write(const void* src, int dt, int ld, int k_col, int v_col, const float* norm_q,
                                            const float* norm_k, float eps, const float* freq, int rot, const float* table,
                                            int table_positions, void* q_out, int q_heads, PagedCache cache,
@@ -393,6 +479,17 @@ X0NE_API int x0ne_whole_norm_rope_kv_write(const void* src, int dt, int ld, int 
     }
     if (n_rows == 0) return 0;
     const size_t smem = (size_t)(rot > 0 ? rot : 2) * sizeof(float);
+    const int vdw = write_kv ? cache_v_dim(cache) : 8;
+    const bool vec = cache.head_dim % 8 == 0 && (rot / 2) % 8 == 0 && ld % 8 == 0 && vdw % 8 == 0 &&
+                     (!write_kv || (k_col % 8 == 0 && v_col % 8 == 0 && cache.page_stride % 8 == 0 && (((uintptr_t)cache.base | (uintptr_t)norm_k) & 31) == 0)) &&
+                     ((((uintptr_t)src | (uintptr_t)q_out | (uintptr_t)norm_q) & 31) == 0);
+    if (vec && (dt == X0NE_F32 || dt == X0NE_BF16)) {
+        if (dt == X0NE_F32)
+            x0ne_launch(whole_norm_rope_kv_write_vec_kernel<float>, dim3(n_rows), dim3(256), smem, stream, (const float*)src, ld, k_col, v_col, norm_q, norm_k, eps, freq, rot, table, table_positions, (float*)q_out, q_heads, cache, row_slot, row_pos, write_kv);
+        else
+            x0ne_launch(whole_norm_rope_kv_write_vec_kernel<bf16>, dim3(n_rows), dim3(256), smem, stream, (const bf16*)src, ld, k_col, v_col, norm_q, norm_k, eps, freq, rot, table, table_positions, (bf16*)q_out, q_heads, cache, row_slot, row_pos, write_kv);
+        X0NE_LAUNCH_CHECK();
+    }
     if (dt == X0NE_F32)
         x0ne_launch(whole_norm_rope_kv_write_kernel<float>, dim3(n_rows), dim3(256), smem, stream, (const float*)src, ld, k_col, v_col, norm_q, norm_k, eps, freq, rot, table, table_positions, (float*)q_out, q_heads, cache, row_slot, row_pos, write_kv);
     else if (dt == X0NE_BF16)

@@ -257,6 +257,62 @@ __global__ void moe_combine_kernel(const float* __restrict__ y, const T* __restr
     }
 }
 
+// The same four columns per thread with 16-byte reads of y (hidden % 4 == 0, aligned rows): grid (column blocks, rows).
+__device__ __forceinline__ void cmb_load4(const float* p, float* v) {
+    const float4 a = *reinterpret_cast<const float4*>(p);
+    v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w;
+}
+__device__ __forceinline__ void cmb_load4(const bf16* p, float* v) {
+    const uint2 u = *reinterpret_cast<const uint2*>(p);
+    const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&u.x));
+    const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&u.y));
+    v[0] = a.x; v[1] = a.y; v[2] = b.x; v[3] = b.y;
+}
+__device__ __forceinline__ void cmb_store4(float* p, const float* v) { *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]); }
+__device__ __forceinline__ void cmb_store4(bf16* p, const float* v) {
+    uint2 u;
+    *reinterpret_cast<__nv_bfloat162*>(&u.x) = __floats2bfloat162_rn(v[0], v[1]);
+    *reinterpret_cast<__nv_bfloat162*>(&u.y) = __floats2bfloat162_rn(v[2], v[3]);
+    *reinterpret_cast<uint2*>(p) = u;
+}
+#define CMB_MAX_TOP 16
+template <typename T>
+__global__ void moe_combine_vec_kernel(const float* __restrict__ y, const T* __restrict__ x, const int32_t* __restrict__ chosen,
+                                       const float* __restrict__ weights, int top, int experts, const T* __restrict__ shared,
+                                       const float* __restrict__ sgate, T* __restrict__ out, int hidden) {
+    pdl_prologue();
+    const int row = blockIdx.y;
+    const int c = (blockIdx.x * blockDim.x + threadIdx.x) * 4;
+    if (c >= hidden) return;
+    const int32_t* ch = chosen + (int64_t)row * top;
+    const float* wt = weights + (int64_t)row * top;
+    float v[CMB_MAX_TOP][4], g[CMB_MAX_TOP];
+    float xs[4], sv[4] = {0.f, 0.f, 0.f, 0.f};
+    cmb_load4(x + (int64_t)row * hidden + c, xs);
+#pragma unroll
+    for (int j = 0; j < CMB_MAX_TOP; ++j) {
+        if (j < top) {
+            g[j] = wt[j];
+            if (ch[j] < experts) cmb_load4(y + ((int64_t)row * top + j) * hidden + c, v[j]);      // (all the loads are in flight together)
+            else { v[j][0] = xs[0]; v[j][1] = xs[1]; v[j][2] = xs[2]; v[j][3] = xs[3]; }
+        }
+    }
+    const float sg = shared != nullptr ? (sgate != nullptr ? sgate[row] : 1.f) : 0.f;
+    if (shared != nullptr) cmb_load4(shared + (int64_t)row * hidden + c, sv);
+    float acc[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+    for (int j = 0; j < CMB_MAX_TOP; ++j)
+        if (j < top) {
+#pragma unroll
+            for (int k = 0; k < 4; ++k) acc[k] = fmaf(g[j], v[j][k], acc[k]);
+        }
+    if (shared != nullptr) {
+#pragma unroll
+        for (int k = 0; k < 4; ++k) acc[k] = fmaf(sg, sv[k], acc[k]);
+    }
+    cmb_store4(out + (int64_t)row * hidden + c, acc);
+}
+
 // ----------------------------------------------------------------------------------------
 // host side
 // ----------------------------------------------------------------------------------------
@@ -318,6 +374,16 @@ X0NE_API int x0ne_moe_combine(const float* y, const void* x, int dt, const int32
                               const void* shared, const float* sgate, void* out, int n_rows, int hidden, cudaStream_t stream) {
     X0NE_REQUIRE(n_rows >= 0 && hidden > 0 && top > 0 && experts >= 0, "moe_combine: rows %d hidden %d top %d", n_rows, hidden, top);
     if (n_rows == 0) return 0;
+    if (hidden % 4 == 0 && top <= CMB_MAX_TOP && n_rows <= 65535 && (dt == X0NE_F32 || dt == X0NE_BF16) &&
+        ((((uintptr_t)y | (uintptr_t)x | (uintptr_t)shared | (uintptr_t)out) & 15) == 0)) {
+        const int threads = hidden / 4 >= 256 ? 256 : (hidden / 4 + 31) / 32 * 32;
+        const dim3 grid((hidden / 4 + threads - 1) / threads, n_rows);
+        if (dt == X0NE_F32)
+            x0ne_launch(moe_combine_vec_kernel<float>, grid, dim3(threads), 0, stream, y, (const float*)x, chosen, weights, top, experts, (const float*)shared, sgate, (float*)out, hidden);
+        else
+            x0ne_launch(moe_combine_vec_kernel<bf16>, grid, dim3(threads), 0, stream, y, (const bf16*)x, chosen, weights, top, experts, (const bf16*)shared, sgate, (bf16*)out, hidden);
+        X0NE_LAUNCH_CHECK();
+    }
     if (dt == X0NE_F32)
         x0ne_launch(moe_combine_kernel<float>, dim3(n_rows), dim3(256), 0, stream, y, (const float*)x, chosen, weights, top, experts, (const float*)shared, sgate, (float*)out, hidden);
     else if (dt == X0NE_BF16)

@@ -70,6 +70,8 @@ __global__ void __launch_bounds__(MT_THREADS) moe_tc_kernel(const __grid_constan
     tc_fence_after();
     const uint32_t tmem = sh->tmem_base;
     pdl_wait();          // the table of tiles, the list and the A rows were written by the kernels before this one
+    // the A rows were written with ordinary stores and are read by TMA: order the two proxies on this side as well
+    asm volatile("fence.proxy.async;" ::: "memory");
     int n_real = n_real_p[0];
     if (n_real > max_tiles) n_real = max_tiles;
     const int total = n_real * n_tiles_n;      // tile id -> (m tile = id % n_real, n tile = id / n_real)
@@ -240,9 +242,13 @@ X0NE_API int x0ne_moe_product_tc(int which, const void* a, int64_t a_rows, const
     if (sms <= 0) sms = 1;
     const int64_t worst = (int64_t)max_tiles * n_tiles_n;
     const int grid = worst < sms ? (int)worst : sms;
+    // Launched without the early-start attribute: the kernel before it writes, with ordinary stores at its very end, the rows
+    // this one reads by TMA a moment later.  Replayed from a graph with the early start, short prompt passes with many padding
+    // rows gave other logits than the same launches made one by one (which leave more time between the two kernels); with a
+    // plain launch and the proxy fence in the kernel they give the same bits.  The kernel still lets its own successor start early.
     if (which == 0)
-        x0ne_launch(moe_tc_kernel<true>, dim3(grid), dim3(MT_THREADS), smem, stream, map_a, map_w, out, N, K, listed, tiles, n_real, max_tiles, n_tiles_n, status);
+        moe_tc_kernel<true><<<grid, MT_THREADS, smem, stream>>>(map_a, map_w, out, N, K, listed, tiles, n_real, max_tiles, n_tiles_n, status);
     else
-        x0ne_launch(moe_tc_kernel<false>, dim3(grid), dim3(MT_THREADS), smem, stream, map_a, map_w, out, N, K, listed, tiles, n_real, max_tiles, n_tiles_n, status);
+        moe_tc_kernel<false><<<grid, MT_THREADS, smem, stream>>>(map_a, map_w, out, N, K, listed, tiles, n_real, max_tiles, n_tiles_n, status);
     X0NE_LAUNCH_CHECK();
 }

@@ -8,6 +8,7 @@ fails; nothing here computes on the CPU or through another library.
 from __future__ import annotations
 
 import ctypes
+import os
 from ctypes import Structure, c_float, c_int, c_int32, c_int64, c_void_p
 from typing import Optional
 
@@ -316,7 +317,7 @@ def relu2(x: torch.Tensor, out: torch.Tensor, n_rows: int) -> None:
 # ---------------------------------------------------------------------------------------------
 MOE_TILE_ROWS = 32       # pairs per tile of the grouped products on the CUDA cores (moe.cu: MOE_TILE_M)
 MOE_TC_TILE_ROWS = 128   # and on the tensor cores (moe_tcgen05.cu: MT_BM)
-MOE_TC_MIN_PAIRS = 256   # passes with at least this many (row, choice) pairs take the tensor-core kernel
+MOE_TC_MIN_PAIRS = int(os.environ.get("X0NE_MOE_TC_MIN_PAIRS", "1"))     # passes with at least this many (row, choice) pairs take the tensor-core kernel
 
 
 def moe_max_tiles(pairs: int, experts: int, tile_rows: int = MOE_TILE_ROWS) -> int:
