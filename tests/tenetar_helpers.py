@@ -60,7 +60,7 @@ CONFIGS = {
                              layer(attention(dim=16, heads=4, kv_heads=4, vdim=24, window=64, keep=1, rot=16), moe(groups=None, identity=0, top=2)),
                              layer(attention(dim=16, heads=8, kv_heads=4, vdim=24, window=9, keep=0, rot=16, kv_from=2), None)]),
     # widths that are multiples of 16, as served models have; one layer without a window, one without rotation
-    "even": lambda: config([layer(attention(dim=32, heads=4, kv_heads=2, vdim=32, window=None, rot=32), moe(experts=8, identity=0, top=2, groups=(2, 1), ff=64, shared=64)),
+    "even": lambda: config([layer(attention(dim=32, heads=4, kv_heads=2, vdim=32, window=None, rot=32), moe(experts=6, identity=0, top=2, groups=(3, 1), ff=64, shared=64)),
                             layer(attention(dim=32, heads=4, kv_heads=2, vdim=32, window=130, keep=64, rot=None), dense(128)),
                             layer(attention(dim=32, heads=4, kv_heads=2, vdim=32, window=100, keep=5, rot=None, kv_from=1), moe(experts=4, identity=4, top=4, groups=(2, 2), ff=32, shared=None))],
                            vocab=256, width=128, scale=1.0),

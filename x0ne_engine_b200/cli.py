@@ -25,6 +25,7 @@ Commands and their options follow the reference's own programs where it has them
       with the time from the end of the kernel before it to its own end (what it adds to the step)
       and its own duration, summed per kernel and listed for one layer in the middle of the model
   kernel-bench --kernel NAME [sizes] [--impl ours|reference]   times one kernel alone with CUDA events
+                (also moe_experts, whole_norm_rope, add_normed_rmsnorm)
       (attention_flex_prefill / attention_flex_decode take --v-dim, --chunk and --latent-rank)
       (the reference's per-kernel timing entry: x0ne-core/runtime/src/ops.rs:579-681).  With
       `--impl reference` the reference project's own kernel of that name (attention_decode,
@@ -494,6 +495,69 @@ def cmd_kernel_bench(a) -> int:
                                                      1 / math.sqrt(hd), 0, extra),
                   T * qh * (hd + out_vd) * 2 + T * kvh * (hd + vd) * 2, 2.0 * qh * (hd + out_vd) * pairs)
         return 0
+    if a.kernel == "moe_experts":
+        # the experts' part of a routed feed-forward: grouping, gather, up product with the squared ReLU, down product;
+        # --m rows, --k width, --n expert width, --experts, --top; every row chooses --top different experts at random
+        rows, hidden, ff, E, top = a.m, a.k, a.n, a.experts, a.top
+        pairs = rows * top
+        wbytes = 2 * E * ff * hidden * 2
+        copies = max(2, int(math.ceil(256e6 / wbytes)) + 1)
+        ups = [torch.randn(E, ff, hidden, device=dev).mul_(0.02).bfloat16() for _ in range(copies)]
+        downs = [torch.randn(E, hidden, ff, device=dev).mul_(0.02).bfloat16() for _ in range(copies)]
+        x = torch.randn(rows, hidden, device=dev).bfloat16()
+        chosen = torch.stack([torch.randperm(E, device=dev)[:top] for _ in range(rows)]).to(torch.int32).contiguous()
+        i32 = lambda *shape: torch.empty(shape, dtype=torch.int32, device=dev)      # noqa: E731
+        tc = ops.moe_tc_takes(torch.bfloat16, pairs, hidden, ff)
+        tile = ops.MOE_TC_TILE_ROWS if tc else ops.MOE_TILE_ROWS
+        n_tiles = ops.moe_max_tiles(pairs, E, tile)
+        offsets, listed, tiles, n_real = i32(E + 1), i32(pairs), i32(n_tiles, 3), i32(1)
+        xs = torch.zeros(pairs, hidden, device=dev, dtype=torch.bfloat16)
+        act = torch.empty(pairs, ff, device=dev, dtype=torch.bfloat16)
+        y = torch.empty(pairs, hidden, device=dev, dtype=torch.float32)
+        turn = [0]
+
+        def run():
+            i = turn[0] = (turn[0] + 1) % copies
+            ops.moe_group(chosen, pairs, E, offsets, listed, tiles, tile, n_real)
+            if tc:
+                ops.moe_gather_rows(x, listed, offsets, E, top, xs, pairs)
+                ops.moe_product_tc(0, xs, ups[i], listed, tiles, n_real, n_tiles, act)
+                ops.moe_product_tc(1, act, downs[i], listed, tiles, n_real, n_tiles, y)
+            else:
+                ops.moe_product(0, x, ups[i], listed, tiles, n_tiles, top, act)
+                ops.moe_product(1, act, downs[i], listed, tiles, n_tiles, top, y)
+        distinct = int(torch.unique(chosen).numel())
+        timed(run, distinct * 2 * ff * hidden * 2 + pairs * (hidden * 2 * 2 + ff * 2 * 2 + hidden * 4), 4.0 * pairs * ff * hidden)
+        return 0
+    if a.kernel == "add_normed_rmsnorm":
+        rows, h = a.m, a.n
+        resid = torch.randn(rows, h, device=dev)
+        delta = torch.randn(rows, h, device=dev).bfloat16()
+        w = torch.ones(h, device=dev)
+        out = torch.empty_like(delta)
+        copies = 1
+        timed(lambda: ops.add_normed_rmsnorm(resid, delta, w, 1e-6, w, out, rows, 1e-6), rows * h * (4 + 4 + 2 + 2))
+        return 0
+    if a.kernel == "whole_norm_rope":
+        # queries and keys normed over the whole projection, rotated, keys and values into the pages; --m rows of one sequence
+        from .cache import SequenceCache
+        from .parts.base import CacheNeed
+        rows, qh, kvh, hd = a.m, a.q_heads, a.kv_heads, a.head_dim
+        cache = SequenceCache([CacheNeed("kv", kvh, hd, None)], [None], rows + 64, rows + 64, torch.bfloat16, dev)
+        slot = cache.acquire(rows)
+        src = torch.randn(rows, (qh + 2 * kvh) * hd, device=dev).bfloat16()
+        q_out = torch.empty(rows, qh * hd, device=dev, dtype=torch.bfloat16)
+        wq, wk = torch.ones(qh * hd, device=dev), torch.ones(kvh * hd, device=dev)
+        freq = (1e6 ** (-torch.arange(0, hd, 2, device=dev, dtype=torch.float32) / hd)).contiguous()
+        slots = torch.full((rows,), slot, dtype=torch.int32, device=dev)
+        pos = torch.arange(rows, dtype=torch.int32, device=dev)
+        ang = pos.float()[:, None] * freq[None, :]
+        table = torch.cat([torch.cos(ang), torch.sin(ang)], dim=1).contiguous()     # [positions, hd]: cosines, then sines
+        copies = 1
+        timed(lambda: ops.whole_norm_rope_kv_write(src, qh * hd, (qh + kvh) * hd, wq, wk, 1e-6, freq, hd, table, q_out, qh,
+                                                   cache.kv_view(0), slots, pos, rows, True),
+              rows * ((qh + 2 * kvh) * hd * 2 + qh * hd * 2 + 2 * kvh * hd * 2))
+        return 0
     if a.kernel == "glu_clipped":
         rows, inter = a.m, a.n
         gu = torch.randn(rows, 2 * inter, device=dev).bfloat16()
@@ -780,6 +844,8 @@ def main(argv=None) -> int:
                    help="attention_decode: with --splits, how many thread-block clusters the splits of a (sequence, kv head) form")
     k.add_argument("--layers", type=int, default=36, help="decode_step (--impl reference): layers of the model")
     k.add_argument("--vocab", type=int, default=151936, help="decode_step (--impl reference): vocabulary")
+    k.add_argument("--experts", type=int, default=16, help="moe_experts: experts of the layer")
+    k.add_argument("--top", type=int, default=4, help="moe_experts: experts a row chooses")
     k.add_argument("--iters", type=int, default=50)
     k.add_argument("--warmup", type=int, default=5)
     k.set_defaults(fn=cmd_kernel_bench)
