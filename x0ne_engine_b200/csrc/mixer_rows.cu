@@ -565,8 +565,9 @@ X0NE_API int x0ne_whole_norm_rope_kv_write(const void* src, int dt, int ld, int 
 #define X0NE_WNR(T, STAGE, SMEM) x0ne_launch(whole_norm_rope_kv_write_vec_kernel<T, STAGE>, dim3(n_rows), dim3(256), SMEM, stream, (const T*)src, ld, k_col, v_col, norm_q, norm_k, eps, freq, rot, table, table_positions, (T*)q_out, q_heads, cache, row_slot, row_pos, write_kv)
         // few rows (decode, short prompts): the staged form, which has the shortest path through a row (3.4 against 3.9 us at 8 rows);
         // many rows: the form that keeps few registers and so more rows in flight (98 against 166 us at 8,192 rows)
-        if (n_rows <= 256 && staged <= 48 * 1024 && (q_heads + (write_kv ? cache.kv_heads : 0)) * cache.head_dim <= WN_MAX_PIECES * 256 * 8) {
-            if (dt == X0NE_F32) X0NE_WNR(float, true, staged); else X0NE_WNR(bf16, true, staged);
+        // (bfloat16 only: in float32 a row's bits must not depend on how many rows share its pass, and the two forms add in other orders)
+        if (dt == X0NE_BF16 && n_rows <= 256 && staged <= 48 * 1024 && (q_heads + (write_kv ? cache.kv_heads : 0)) * cache.head_dim <= WN_MAX_PIECES * 256 * 8) {
+            X0NE_WNR(bf16, true, staged);
         } else {
             if (dt == X0NE_F32) X0NE_WNR(float, false, head); else X0NE_WNR(bf16, false, head);
         }
