@@ -72,6 +72,12 @@ CONFIGS = {
     "odd": lambda: config([layer(attention(dim=10, heads=3, kv_heads=3, vdim=6, window=11, keep=2, rot=6), moe(experts=3, identity=3, top=2, groups=(3, 2), ff=50, shared=14)),
                            layer(attention(dim=10, heads=3, kv_heads=3, vdim=6, window=40, keep=13, rot=6, kv_from=0), dense(50))],
                           vocab=101, width=100),
+    # sizes of a small served model: heads of 64 with half of each rotated, 16 + 4 experts in 4 groups, 6 chosen
+    "served": lambda: config([layer(attention(dim=64, heads=8, kv_heads=2, vdim=64, window=128, keep=8, rot=32, base=500000.0), dense(512)),
+                              layer(attention(dim=64, heads=8, kv_heads=2, vdim=64, window=128, keep=8, rot=32, base=500000.0), moe(experts=16, identity=4, top=6, groups=(4, 2), ff=128, shared=192)),
+                              layer(attention(dim=64, heads=8, kv_heads=2, vdim=64, window=200, keep=0, rot=32, base=500000.0, kv_from=1), moe(experts=16, identity=4, top=6, groups=(4, 2), ff=128, shared=192)),
+                              layer(attention(dim=128, heads=4, kv_heads=4, vdim=128, window=96, keep=65, rot=128), moe(experts=4, identity=0, top=1, groups=None, ff=256, shared=None))],
+                             vocab=1000, width=256, scale=16.0),
     "attention_only": lambda: config([layer(attention(window=9, keep=2), None)]),
     "dense_only": lambda: config([layer(attention(heads=2, kv_heads=1, dim=8, vdim=8, window=5, keep=1, rot=8), dense(160))]),
     "experts_only": lambda: config([layer(attention(heads=2, kv_heads=1, dim=8, vdim=8, window=None, rot=None), moe())]),

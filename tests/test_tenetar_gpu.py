@@ -371,7 +371,7 @@ def test_attention_kernels_with_kept_first_keys(case):
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("name,lengths", [("attention_only", [1, 2, 9, 10, 40]), ("dense_only", [1, 12]), ("experts_only", [1, 3, 70]),
                                           ("mixed", [1, 2, 37, 38, 65, 150]), ("even", [64, 131, 300]), ("wide", [5, 71, 141]),
-                                          ("odd", [1, 12, 90])])
+                                          ("odd", [1, 12, 90]), ("served", [7, 450])])
 def test_each_request_alone_and_whole(name, lengths, dtype):
     eng, cfg, t = engine(name, dtype)
     for k, n in enumerate(lengths):
@@ -414,7 +414,7 @@ def test_soft_routing_in_float32():
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("name,n,tail", [("mixed", 120, 60), ("wide", 100, 40), ("even", 160, 40), ("odd", 70, 30)])
+@pytest.mark.parametrize("name,n,tail", [("mixed", 120, 60), ("wide", 100, 40), ("even", 160, 40), ("odd", 70, 30), ("served", 330, 140)])
 def test_prefill_against_token_by_token(name, n, tail, dtype):
     eng, cfg, t = engine(name, dtype)
     ids = ids_for(cfg, t, n, dtype, seed=5)
